@@ -1,0 +1,72 @@
+"""Shared helpers for the parity tests."""
+from __future__ import annotations
+
+import os
+
+import numpy as np
+import torch
+
+from cases import CASES, CASES_BY_NAME, DTYPES, make_inputs  # noqa: F401  (tests/golden on sys.path)
+from make_golden import sample_positions, to_bits
+
+GOLDEN_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "golden.npz")
+_golden = None
+
+
+def golden():
+    global _golden
+    if _golden is None:
+        _golden = np.load(GOLDEN_PATH)
+    return _golden
+
+
+def golden_sample(name):
+    return golden()[f"{name}/out"]
+
+
+def sample_of(out: torch.Tensor) -> np.ndarray:
+    flat = to_bits(out.cpu()).reshape(-1)
+    return flat[sample_positions(flat.size)]
+
+
+def bits_to_float(bits: np.ndarray, dtype: str) -> np.ndarray:
+    """Decode a stored sample to float64."""
+    if dtype == "f32":
+        return bits.astype(np.float64)
+    t = torch.from_numpy(bits.astype(np.int16)).view(DTYPES[dtype])
+    return t.to(torch.float64).numpy()
+
+
+def error_metrics(got, ref):
+    """max-abs, max-abs relative to max|ref|, relative Frobenius."""
+    got = np.asarray(got, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    d = got - ref
+    scale = max(float(np.abs(ref).max()), 1e-30)
+    fro = float(np.sqrt((d * d).sum()) / max(np.sqrt((ref * ref).sum()), 1e-30))
+    return float(np.abs(d).max()), float(np.abs(d).max() / scale), fro
+
+
+# Tolerances.  fp32: 1e-4 relative (max-abs error over max-abs reference, and
+# relative Frobenius).  bf16: 2e-2 max-abs, plus a relative Frobenius bound
+# because max-abs alone is vacuous for small-magnitude outputs.  fp16: the
+# reference's own test tolerance of 1e-2 (ma/tests/test_ma.py:64-65) plus a
+# relative Frobenius bound.
+TOL = {
+    "f32": dict(max_abs=None, rel_max=1e-4, fro=1e-4),
+    "bf16": dict(max_abs=2e-2, rel_max=None, fro=1.5e-2),
+    "f16": dict(max_abs=1e-2, rel_max=None, fro=4e-3),
+}
+
+
+def check_close(got, ref, dtype: str, what: str = ""):
+    mabs, mrel, fro = error_metrics(got, ref)
+    t = TOL[dtype]
+    msg = f"{what}: max_abs={mabs:.3e} rel_max={mrel:.3e} rel_fro={fro:.3e} (dtype {dtype})"
+    assert np.isfinite(np.asarray(got, dtype=np.float64)).all(), "non-finite output " + msg
+    if t["max_abs"] is not None:
+        assert mabs <= t["max_abs"], msg
+    if t["rel_max"] is not None:
+        assert mrel <= t["rel_max"], msg
+    assert fro <= t["fro"], msg
+    return mabs, mrel, fro
