@@ -1,0 +1,131 @@
+/*
+ * monarch_attention_b200 - C ABI of the B200 (sm_100a) MonarchAttention forward library.
+ *
+ * This is the boundary a binding of the reference's attention module links against.
+ * Every entry point takes plain pointers, sizes and a stream handle; no framework types.
+ *
+ * What it replaces in the reference:
+ *   - an implementation function as registered with the module
+ *     (reference: ma/monarch_attention.py:11-19, signature
+ *      fn(q, k, v, attn_mask | None, T, B, pre_pad) -> Tensor), i.e.
+ *     monarch_attention_torch (reference: ma/ma_torch.py:65-108) and
+ *     monarch_attention_triton (reference: ma/ma_triton.py:641-788);
+ *   - the four stage functions that call evaluates
+ *     (reference: ma/ma_torch.py:10-23, :26-35, :38-52, :55-62).
+ *
+ * Memory ownership: the caller owns q, k, v, out, mask and the workspace (all device
+ * memory of the current device).  The library allocates no device memory in
+ * ma_b200_forward.  Work is enqueued on the given stream and is stream-ordered.
+ *
+ * Tensors are 4-D views (E, H, N, W) whose innermost stride is 1 element; the other
+ * three strides are arbitrary element strides (so a permuted (E, N, H, W) buffer is
+ * accepted without a copy).
+ */
+#ifndef MONARCH_ATTENTION_B200_H_
+#define MONARCH_ATTENTION_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MA_B200_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define MA_B200_API __attribute__((visibility("default")))
+#else
+#define MA_B200_API
+#endif
+
+/* Return codes of every entry point that returns int. */
+enum {
+  MA_B200_OK = 0,
+  MA_B200_INVALID_ARGUMENT = 1, /* NULL pointer, bad shape / stride / alignment / dtype       */
+  MA_B200_UNSUPPORTED = 2,      /* valid problem that the requested kernel cannot run         */
+  MA_B200_CUDA_ERROR = 3,       /* a CUDA runtime / driver call failed (see last_error)       */
+  MA_B200_DEVICE_WAIT_EXPIRED = 4, /* a bounded on-device wait gave up; output is undefined   */
+  MA_B200_WORKSPACE_TOO_SMALL = 5
+};
+
+/* Element types.  q and k share qk_dtype; v and out share v_dtype. */
+enum { MA_B200_F32 = 0, MA_B200_BF16 = 1, MA_B200_F16 = 2 };
+
+/* Kernel families.  AUTO picks the tensor-core path when the problem fits it. */
+enum { MA_B200_KERNEL_AUTO = 0, MA_B200_KERNEL_GENERIC = 1, MA_B200_KERNEL_TCGEN05 = 2 };
+
+typedef struct ma_b200_tensor {
+  void* ptr;        /* device pointer to element (0,0,0,0)            */
+  int64_t stride_e; /* element strides; the innermost stride is 1     */
+  int64_t stride_h;
+  int64_t stride_n;
+} ma_b200_tensor;
+
+/*
+ * One forward call.  Field meaning follows the reference's implementation-function
+ * arguments (reference: ma/ma_torch.py:65-73): num_steps = T, block_size = B,
+ * pre_pad != 0 pads the token axis at the front.  mask is the (E, N) key/query
+ * validity mask, one byte per token, non-zero = valid, or NULL
+ * (reference: ma/ma_torch.py:96-98 combines it with the padding mask).
+ */
+typedef struct ma_b200_problem {
+  int32_t abi_version; /* MA_B200_ABI_VERSION */
+  int32_t E, H, N, D, Dv;
+  int32_t block_size;
+  int32_t num_steps;
+  int32_t pre_pad;
+  int32_t qk_dtype;
+  int32_t v_dtype;
+  int32_t kernel; /* MA_B200_KERNEL_* */
+  ma_b200_tensor q, k, v, out;
+  const uint8_t* mask;
+  int64_t mask_stride_e;
+} ma_b200_problem;
+
+/* Byte offsets of the stage-to-stage state inside the workspace (for tests and tools).
+ * ar: (E*H, M, B, D) qk_dtype   cr: (E*H, M, B) f32
+ * al: (E*H, B, M, D) qk_dtype   cl: (E*H, B, M) f32   y: (E*H, B, M, Dv) v_dtype
+ * status: one int32 device flag, 0 = no device-side error. */
+typedef struct ma_b200_workspace_layout {
+  size_t status, ar, cr, al, cl, y, total;
+  int32_t M;
+  int32_t kernel; /* the family AUTO resolves to */
+} ma_b200_workspace_layout;
+
+/* Scratch bytes ma_b200_forward needs for this problem (0 on an invalid problem).
+ * The workspace must be 256-byte aligned.
+ * reference: the Triton launcher allocates the same state per call (ma/ma_triton.py:669-676,734). */
+MA_B200_API size_t ma_b200_workspace_bytes(const ma_b200_problem* p);
+
+/* Fill *layout; returns MA_B200_OK or an error code. */
+MA_B200_API int ma_b200_workspace_layout_of(const ma_b200_problem* p, ma_b200_workspace_layout* layout);
+
+/* Enqueue the forward pass on `stream` (a cudaStream_t / CUstream; NULL = default stream).
+ * reference: monarch_attention_torch, ma/ma_torch.py:65-108. */
+MA_B200_API int ma_b200_forward(const ma_b200_problem* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Same as ma_b200_forward, and additionally records one CUDA event pair per stage launch
+ * and, after synchronising the stream, writes the stage durations in milliseconds to
+ * stage_ms[0 .. min(n_stage_ms, 2*num_steps) - 1] in launch order.  Blocks the host.
+ * reference: the per-kernel NVTX/ncu harness, perfbench/bench.py:199-223. */
+MA_B200_API int ma_b200_forward_timed(const ma_b200_problem* p, void* workspace, size_t workspace_bytes, void* stream,
+                          float* stage_ms, int32_t n_stage_ms);
+
+/* Synchronise `stream` and read the device-side status flag of the last forward that used
+ * this workspace: MA_B200_OK or MA_B200_DEVICE_WAIT_EXPIRED. */
+MA_B200_API int ma_b200_device_status(void* workspace, void* stream);
+
+/* Human-readable text for a return code. */
+MA_B200_API const char* ma_b200_status_string(int status);
+
+/* Detail of the last failure on the calling thread ("" if none). */
+MA_B200_API const char* ma_b200_last_error(void);
+
+/* Library ABI version (MA_B200_ABI_VERSION at build time). */
+MA_B200_API int32_t ma_b200_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MONARCH_ATTENTION_B200_H_ */

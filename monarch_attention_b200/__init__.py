@@ -1,0 +1,4 @@
+"""B200 (sm_100a) MonarchAttention forward library behind the reference's module API."""
+from .monarch_attention import MonarchAttention, PadType, monarch_attention_b200, register_impl
+
+__all__ = ["MonarchAttention", "PadType", "monarch_attention_b200", "register_impl"]

@@ -1,0 +1,82 @@
+// Shared definitions for the MonarchAttention kernels (sm_100a).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/monarch_attention_b200.h"
+
+namespace ma {
+
+constexpr float kEps = 1e-12f;            // eps of the right-factor stages (reference: ma/ma_torch.py:10)
+constexpr float kTiny = 1.17549435e-38f;  // smallest normal fp32: floor of the right-factor entries (:18)
+
+// A strided (E,H,N,W) view; strides in elements, innermost stride 1.
+struct View4 {
+  const void* ptr;
+  long long se, sh, sn;
+};
+
+// Everything a stage kernel needs to know about one forward call.
+struct Geometry {
+  int E, H, N, D, Dv;
+  int B, M;        // block size, number of blocks
+  int pad_off;     // padded position p = m*B + j maps to token p - pad_off
+  int T;
+  float sm_scale;  // (float)(1/sqrt(D))
+  View4 q, k, v, out;
+  const uint8_t* mask;  // (E,N) bytes, non-zero = valid; or nullptr
+  long long mask_se;
+  // stage-to-stage state (workspace)
+  void* ar;   // (EH, M, B, D)  qk dtype
+  float* cr;  // (EH, M, B)
+  void* al;   // (EH, B, M, D)  qk dtype
+  float* cl;  // (EH, B, M)
+  void* y;    // (EH, B, M, Dv) v dtype
+  int* status;  // device flag, 0 = fine
+};
+
+enum StageKind { kStageRight = 0, kStageRightWithV = 1, kStageLeft = 2, kStageOutput = 3 };
+
+template <typename T>
+struct Cvt;
+template <>
+struct Cvt<float> {
+  static __device__ __forceinline__ float to_f(float x) { return x; }
+  static __device__ __forceinline__ float from_f(float x) { return x; }
+};
+template <>
+struct Cvt<__nv_bfloat16> {
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 x) { return __bfloat162float(x); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float x) { return __float2bfloat16_rn(x); }
+};
+template <>
+struct Cvt<__half> {
+  static __device__ __forceinline__ float to_f(__half x) { return __half2float(x); }
+  static __device__ __forceinline__ __half from_f(float x) { return __float2half_rn(x); }
+};
+
+// Round an fp32 value through storage type T and back (the reference rounds every
+// contraction result to the storage dtype before the fp32 softmax arithmetic).
+template <typename T>
+__device__ __forceinline__ float round_through(float x) {
+  return Cvt<T>::to_f(Cvt<T>::from_f(x));
+}
+
+// Host-side launchers implemented by the kernel translation units.
+// Each returns cudaSuccess or the launch error.
+cudaError_t launch_generic_stage(const Geometry& g, int qk_dtype, int v_dtype, StageKind kind, bool first,
+                                 cudaStream_t stream);
+size_t generic_stage_smem_bytes(const Geometry& g, StageKind kind);
+
+// Tensor-core (tcgen05) path.
+bool tc_supported(const Geometry& g, int qk_dtype, int v_dtype, const char** why);
+// Prepares per-call tensor maps; returns an opaque plan used by launch_tc_stage.
+struct TcPlan;
+int tc_plan_create(const Geometry& g, int qk_dtype, TcPlan** plan, const char** err);
+void tc_plan_destroy(TcPlan* plan);
+cudaError_t launch_tc_stage(const TcPlan* plan, const Geometry& g, StageKind kind, bool first, cudaStream_t stream);
+
+}  // namespace ma

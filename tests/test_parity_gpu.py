@@ -1,0 +1,187 @@
+"""Parity of the CUDA library (called through the module API -> C ABI) with the CPU oracle
+and with the committed outputs of the reference.  Needs a B200."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import (CASES, CASES_BY_NAME, DTYPES, bits_to_float, check_close, error_metrics, golden_sample,
+                     make_inputs, sample_of)
+from oracle.monarch_oracle import OracleState, monarch_attention_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ma():
+    import monarch_attention_b200 as pkg
+    from monarch_attention_b200 import _cabi
+    _cabi.load()  # fail loudly if the extension is missing
+    return pkg
+
+
+def _run(ma, case, impl, q, k, v, mask):
+    mod = ma.MonarchAttention(case["B"], case["T"], "pre" if case["pre_pad"] else "post", impl=impl)
+    dev = torch.device("cuda:0")
+    out = mod(q.to(dev), k.to(dev), v.to(dev), None if mask is None else mask.to(dev))
+    torch.cuda.synchronize()
+    return out
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c["name"] for c in CASES])
+def test_generic_kernels_match_oracle_and_golden(ma, case):
+    q, k, v, mask = make_inputs(case)
+    out = _run(ma, case, "b200-generic", q, k, v, mask)
+    assert out.shape == (case["E"], case["H"], case["N"], case["Dv"]) and out.dtype == v.dtype
+    ref = monarch_attention_oracle(q, k, v, mask, case["T"], case["B"], case["pre_pad"])
+    vd = case["vdtype"]
+    check_close(out.double().cpu().numpy(), ref.double().numpy(), vd, case["name"] + " vs oracle")
+    check_close(bits_to_float(sample_of(out), vd), bits_to_float(golden_sample(case["name"]), vd), vd,
+                case["name"] + " vs reference golden")
+
+
+TC_CASES = [c for c in CASES if c["B"] == 128 and c["N"] == 16384 and c["dtype"] in ("bf16", "f16")]
+
+
+@pytest.mark.parametrize("case", TC_CASES, ids=[c["name"] for c in TC_CASES])
+def test_tcgen05_kernels_match_oracle_and_golden(ma, case):
+    q, k, v, mask = make_inputs(case)
+    out = _run(ma, case, "b200-tcgen05", q, k, v, mask)
+    ref = monarch_attention_oracle(q, k, v, mask, case["T"], case["B"], case["pre_pad"])
+    vd = case["vdtype"]
+    check_close(out.double().cpu().numpy(), ref.double().numpy(), vd, case["name"] + " vs oracle")
+    check_close(bits_to_float(sample_of(out), vd), bits_to_float(golden_sample(case["name"]), vd), vd,
+                case["name"] + " vs reference golden")
+
+
+def _state_from_workspace(ma, q, k, v, T, B, kernel):
+    """Run one forward through the C ABI with a private workspace and return (out, state tensors)."""
+    from monarch_attention_b200 import _cabi
+    from monarch_attention_b200.monarch_attention import make_problem
+    lib = _cabi.load()
+    out = torch.empty_like(v)
+    prob = make_problem(q, k, v, out, None, T, B, False, kernel)
+    L = _cabi.WorkspaceLayout()
+    _cabi.raise_for_status(lib.ma_b200_workspace_layout_of(C.byref(prob), C.byref(L)))
+    ws = torch.zeros(L.total, dtype=torch.uint8, device=q.device)
+    rc = lib.ma_b200_forward(C.byref(prob), ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream)
+    _cabi.raise_for_status(rc)
+    _cabi.raise_for_status(lib.ma_b200_device_status(ws.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    E, H, N, D = q.shape
+    M, EH = L.M, E * H
+    es = q.element_size()
+
+    def take(off, shape, dtype):
+        n = int(np.prod(shape)) * torch.empty((), dtype=dtype).element_size()
+        return ws[off:off + n].view(dtype).reshape(shape)
+
+    st = dict(al=take(L.al, (EH, B, M, D), q.dtype), cl=take(L.cl, (EH, B, M), torch.float32),
+              y=take(L.y, (EH, B, M, v.shape[-1]), v.dtype))
+    if T > 1:
+        st.update(ar=take(L.ar, (EH, M, B, D), q.dtype), cr=take(L.cr, (EH, M, B), torch.float32))
+    return out, st, L
+
+
+@pytest.mark.parametrize("name,kernel", [("cfg3_n16384_unit_bf16", 2), ("cfg3_n16384_unit_bf16", 1),
+                                         ("cfg3_n4096_unit_bf16", 1), ("edge_t4_f32", 1)])
+def test_stage_state_matches_oracle(ma, name, kernel):
+    """Every stage-to-stage tensor (ar, cr, al, cl, y), not just the final output."""
+    case = CASES_BY_NAME[name]
+    q, k, v, _ = make_inputs(case)
+    st_ref = OracleState()
+    ref = monarch_attention_oracle(q, k, v, None, case["T"], case["B"], False, state=st_ref)
+    dev = torch.device("cuda:0")
+    out, st, L = _state_from_workspace(ma, q.to(dev), k.to(dev), v.to(dev), case["T"], case["B"], kernel)
+    assert L.kernel == kernel
+    dt = case["dtype"]
+    fro_lim = {"f32": 1e-4, "bf16": 1.5e-2, "f16": 4e-3}[dt]
+    report = {}
+    for key in ("ar", "cr", "al", "cl", "y"):
+        want = getattr(st_ref, key)
+        want = want.reshape(-1, *want.shape[2:]).double().numpy()
+        got = st[key].double().cpu().numpy()
+        report[key] = error_metrics(got, want)
+    msg = " ".join(f"{k}: fro={v[2]:.2e} max={v[0]:.2e}" for k, v in report.items())
+    for key, (mabs, mrel, fro) in report.items():
+        assert np.isfinite(fro) and fro <= fro_lim, f"{name} kernel={kernel} stage tensor {key}: {msg}"
+    check_close(out.double().cpu().numpy(), ref.double().numpy(), dt, name)
+
+
+def test_strided_views_are_read_in_place(ma):
+    """q, k, v handed over as permuted (E, N, H, D) buffers, as the model adapters do
+    (reference: experiments/vit/model.py:73-79)."""
+    case = CASES_BY_NAME["cfg2_vit_bf16"]
+    q, k, v, _ = make_inputs(case)
+    dev = torch.device("cuda:0")
+
+    def permuted(t):
+        buf = t.permute(0, 2, 1, 3).contiguous().to(dev)   # (E, N, H, D) memory
+        return buf.permute(0, 2, 1, 3)                      # (E, H, N, D) view
+
+    mod = ma.MonarchAttention(case["B"], case["T"], "pre")
+    a = mod(permuted(q), permuted(k), permuted(v))
+    b = mod(q.to(dev), k.to(dev), v.to(dev))
+    assert torch.equal(a, b)
+
+
+def test_get_matrix_is_row_stochastic_and_matches_oracle(ma):
+    case = CASES_BY_NAME["edge_matrix_f32v_bf16"]
+    q, k, v, _ = make_inputs(case)
+    dev = torch.device("cuda:0")
+    mod = ma.MonarchAttention(case["B"], case["T"], "post")
+    a = mod.get_matrix(q.to(dev), k.to(dev))
+    assert a.dtype == torch.float32 and a.shape == (1, 2, 36, 36)
+    assert torch.allclose(a.sum(-1), torch.ones_like(a.sum(-1)), atol=1e-3)
+    ref = monarch_attention_oracle(q, k, v, None, case["T"], case["B"], False)
+    assert error_metrics(a.double().cpu().numpy(), ref.double().numpy())[2] < 1.5e-2
+
+
+def test_module_errors_on_gpu(ma):
+    dev = torch.device("cuda:0")
+    q = torch.zeros(1, 2, 32, 16, device=dev)
+    mod = ma.MonarchAttention(8, 2, "post")
+    with pytest.raises(ValueError):
+        mod(q, q[:, :, :16], q)
+    with pytest.raises(ValueError):
+        mod(q, q, q, torch.ones(1, 31, device=dev))
+    with pytest.raises(ValueError, match="tcgen05 path cannot run"):
+        ma.MonarchAttention(8, 2, "post", impl="b200-tcgen05")(q.half(), q.half(), q.half())
+
+
+# ---- full benchmark size: properties that need no CPU oracle run ---------------------------
+
+@pytest.fixture(scope="module")
+def full_inputs():
+    g = torch.Generator(device="cpu").manual_seed(1234)
+    shape = (1, 16, 16384, 64)
+    q, k, v = (torch.randn(shape, generator=g) for _ in range(3))
+    dev = torch.device("cuda:0")
+    return tuple(t.to(torch.bfloat16).to(dev) for t in (q, k, v))
+
+
+@pytest.mark.parametrize("impl", ["b200-tcgen05", "b200-generic"])
+def test_full_size_constant_value_rows(ma, full_inputs, impl):
+    """The Monarch matrix is row-stochastic: with every row of V equal to c, every output row is c."""
+    q, k, _ = full_inputs
+    c = torch.linspace(-2, 2, 64, device=q.device).to(torch.bfloat16)
+    v = c.expand(1, 16, 16384, 64).contiguous()
+    out = ma.MonarchAttention(128, 2, "post", impl=impl)(q, k, v)
+    err = (out.float() - c.float()).abs().max().item()
+    assert err < 3e-2, err
+
+
+def test_full_size_paths_agree_and_heads_permute(ma, full_inputs):
+    q, k, v = full_inputs
+    mod_tc = ma.MonarchAttention(128, 2, "post", impl="b200-tcgen05")
+    mod_gen = ma.MonarchAttention(128, 2, "post", impl="b200-generic")
+    a = mod_tc(q, k, v)
+    b = mod_gen(q, k, v)
+    check_close(a.double().cpu().numpy(), b.double().cpu().numpy(), "bf16", "tcgen05 vs generic, full size")
+    perm = torch.randperm(16, device=q.device)
+    a_p = mod_tc(q[:, perm], k[:, perm], v[:, perm])   # strided head views
+    assert torch.equal(a[:, perm], a_p)
+    # two heads against the CPU oracle
+    for h in (0, 11):
+        ref = monarch_attention_oracle(q[:, h:h + 1].cpu(), k[:, h:h + 1].cpu(), v[:, h:h + 1].cpu(), None, 2, 128, False)
+        check_close(a[:, h:h + 1].double().cpu().numpy(), ref.double().numpy(), "bf16", f"full size head {h}")
