@@ -51,7 +51,10 @@ def error_metrics(got, ref):
 # relative Frobenius).  bf16: 2e-2 max-abs, plus a relative Frobenius bound
 # because max-abs alone is vacuous for small-magnitude outputs.  fp16: the
 # reference's own test tolerance of 1e-2 (ma/tests/test_ma.py:64-65) plus a
-# relative Frobenius bound.
+# relative Frobenius bound.  The max-abs bounds are stated for outputs of unit
+# scale; where the reference output exceeds 1 in magnitude they scale with
+# max|ref| (one bf16 ulp at 3.0 is already 1.6e-2, so a single rounding flip
+# would otherwise fail the absolute bound).
 TOL = {
     "f32": dict(max_abs=None, rel_max=1e-4, fro=1e-4),
     "bf16": dict(max_abs=2e-2, rel_max=None, fro=1.5e-2),
@@ -65,7 +68,7 @@ def check_close(got, ref, dtype: str, what: str = ""):
     msg = f"{what}: max_abs={mabs:.3e} rel_max={mrel:.3e} rel_fro={fro:.3e} (dtype {dtype})"
     assert np.isfinite(np.asarray(got, dtype=np.float64)).all(), "non-finite output " + msg
     if t["max_abs"] is not None:
-        assert mabs <= t["max_abs"], msg
+        assert mabs <= t["max_abs"] * max(1.0, float(np.abs(np.asarray(ref, dtype=np.float64)).max())), msg
     if t["rel_max"] is not None:
         assert mrel <= t["rel_max"], msg
     assert fro <= t["fro"], msg
