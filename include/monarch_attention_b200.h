@@ -122,6 +122,35 @@ MA_B200_API const char* ma_b200_status_string(int status);
 /* Detail of the last failure on the calling thread ("" if none). */
 MA_B200_API const char* ma_b200_last_error(void);
 
+/*
+ * Forward pass for callers that cannot allocate device memory (no counterpart in the
+ * reference, which allocates its state per call).
+ *
+ * Who needs it: a host process that gave all device memory to its own pool at start-up, a
+ * plug-in that must not call the CUDA allocator, a latency-critical loop where an allocator
+ * call is not acceptable.  Such a caller cannot supply the workspace ma_b200_forward wants.
+ * Here the stage-to-stage state lives in a fixed array inside the library image:
+ * MA_B200_STATIC_SCRATCH_BYTES on every GPU that loads the library, held until the process
+ * exits.  The caller passes q, k, v, out and mask exactly as for ma_b200_forward; p->kernel
+ * is ignored and the generic kernel family runs.  Nothing is allocated or freed, on the
+ * device or through any allocating library call.
+ *
+ * Limits and rules:
+ *  - a problem whose state (ma_b200_workspace_bytes with kernel = GENERIC) exceeds
+ *    MA_B200_STATIC_SCRATCH_BYTES is refused with MA_B200_WORKSPACE_TOO_SMALL;
+ *  - the first call on each device looks up the device address of the array (with that
+ *    device current) and caches it; make that first call before any stream capture begins;
+ *  - all calls on one GPU share the one array, which keeps the previous call's contents
+ *    (the library clears the one word that must start at zero): calls that may overlap in
+ *    time on the GPU - different streams, different host threads - race on it and must be
+ *    serialised by the caller; calls queued on a single stream are safe.
+ * Failure detail: ma_b200_static_scratch_last_error().
+ */
+#define MA_B200_STATIC_SCRATCH_BYTES ((size_t)8 << 20)
+MA_B200_API int ma_b200_forward_static_scratch(const ma_b200_problem* p, void* stream);
+MA_B200_API size_t ma_b200_static_scratch_bytes(void);
+MA_B200_API const char* ma_b200_static_scratch_last_error(void);
+
 /* Library ABI version (MA_B200_ABI_VERSION at build time). */
 MA_B200_API int32_t ma_b200_abi_version(void);
 

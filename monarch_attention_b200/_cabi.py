@@ -19,6 +19,7 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libm
 EXPORTS = (
     "ma_b200_workspace_bytes", "ma_b200_workspace_layout_of", "ma_b200_forward", "ma_b200_forward_timed",
     "ma_b200_device_status", "ma_b200_status_string", "ma_b200_last_error", "ma_b200_abi_version",
+    "ma_b200_forward_static_scratch", "ma_b200_static_scratch_bytes", "ma_b200_static_scratch_last_error",
 )
 
 
@@ -72,6 +73,12 @@ def load() -> C.CDLL:
     lib.ma_b200_last_error.restype = C.c_char_p
     lib.ma_b200_abi_version.argtypes = []
     lib.ma_b200_abi_version.restype = C.c_int32
+    lib.ma_b200_forward_static_scratch.argtypes = [pp, C.c_void_p]
+    lib.ma_b200_forward_static_scratch.restype = C.c_int
+    lib.ma_b200_static_scratch_bytes.argtypes = []
+    lib.ma_b200_static_scratch_bytes.restype = C.c_size_t
+    lib.ma_b200_static_scratch_last_error.argtypes = []
+    lib.ma_b200_static_scratch_last_error.restype = C.c_char_p
     if lib.ma_b200_abi_version() != ABI_VERSION:
         raise RuntimeError("libmonarch_attention_b200.so was built for a different ABI version; rebuild it")
     _lib = lib

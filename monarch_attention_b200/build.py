@@ -16,7 +16,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libmonarch_attention_b200.so")
-SOURCES = ["ma_api.cu", "ma_generic.cu", "ma_tc.cu"]
+SOURCES = ["ma_api.cu", "ma_generic.cu", "ma_tc.cu", "ma_noalloc.cu"]
 HEADERS = ["ma_common.cuh", os.path.join("..", "..", "include", "monarch_attention_b200.h")]
 
 NVCC_FLAGS = [
