@@ -52,8 +52,18 @@ enum {
 /* Element types.  q and k share qk_dtype; v and out share v_dtype. */
 enum { MA_B200_F32 = 0, MA_B200_BF16 = 1, MA_B200_F16 = 2 };
 
-/* Kernel families.  AUTO picks the tensor-core path when the problem fits it. */
-enum { MA_B200_KERNEL_AUTO = 0, MA_B200_KERNEL_GENERIC = 1, MA_B200_KERNEL_TCGEN05 = 2 };
+/* Kernel families.  AUTO picks the fused tensor-core kernel when the problem fits it.
+ *   GENERIC        SIMT stage kernels, any shape / dtype / mask (2T launches)
+ *   TCGEN05        persistent tcgen05 kernel, all 2T stages in one launch
+ *   TCGEN05_STAGED the same kernel launched once per stage (for per-stage timing)
+ *   TCGEN05_TILE   one-tile-per-CTA tcgen05 stage kernels (2T launches; cross-check) */
+enum {
+  MA_B200_KERNEL_AUTO = 0,
+  MA_B200_KERNEL_GENERIC = 1,
+  MA_B200_KERNEL_TCGEN05 = 2,
+  MA_B200_KERNEL_TCGEN05_STAGED = 3,
+  MA_B200_KERNEL_TCGEN05_TILE = 4
+};
 
 typedef struct ma_b200_tensor {
   void* ptr;        /* device pointer to element (0,0,0,0)            */
@@ -86,9 +96,10 @@ typedef struct ma_b200_problem {
 /* Byte offsets of the stage-to-stage state inside the workspace (for tests and tools).
  * ar: (E*H, M, B, D) qk_dtype   cr: (E*H, M, B) f32
  * al: (E*H, B, M, D) qk_dtype   cl: (E*H, B, M) f32   y: (E*H, B, M, Dv) v_dtype
- * status: one int32 device flag, 0 = no device-side error. */
+ * status: one int32 device flag, 0 = no device-side error.
+ * counters: (E*H, 2T) int32 stage-completion counters of the fused kernel. */
 typedef struct ma_b200_workspace_layout {
-  size_t status, ar, cr, al, cl, y, total;
+  size_t status, counters, ar, cr, al, cl, y, total;
   int32_t M;
   int32_t kernel; /* the family AUTO resolves to */
 } ma_b200_workspace_layout;
@@ -107,7 +118,8 @@ MA_B200_API int ma_b200_forward(const ma_b200_problem* p, void* workspace, size_
 
 /* Same as ma_b200_forward, and additionally records one CUDA event pair per stage launch
  * and, after synchronising the stream, writes the stage durations in milliseconds to
- * stage_ms[0 .. min(n_stage_ms, 2*num_steps) - 1] in launch order.  Blocks the host.
+ * stage_ms[0 .. min(n_stage_ms, 2*num_steps) - 1] in launch order (the fused kernel has a single
+ * launch: its duration is stage_ms[0], the other entries are 0).  Blocks the host.
  * reference: the per-kernel NVTX/ncu harness, perfbench/bench.py:199-223. */
 MA_B200_API int ma_b200_forward_timed(const ma_b200_problem* p, void* workspace, size_t workspace_bytes, void* stream,
                           float* stage_ms, int32_t n_stage_ms);

@@ -10,8 +10,9 @@ import os
 
 ABI_VERSION = 1
 F32, BF16, F16 = 0, 1, 2
-KERNEL_AUTO, KERNEL_GENERIC, KERNEL_TCGEN05 = 0, 1, 2
-KERNEL_NAMES = {KERNEL_AUTO: "auto", KERNEL_GENERIC: "generic", KERNEL_TCGEN05: "tcgen05"}
+KERNEL_AUTO, KERNEL_GENERIC, KERNEL_TCGEN05, KERNEL_TCGEN05_STAGED, KERNEL_TCGEN05_TILE = 0, 1, 2, 3, 4
+KERNEL_NAMES = {KERNEL_AUTO: "auto", KERNEL_GENERIC: "generic", KERNEL_TCGEN05: "tcgen05-fused",
+                KERNEL_TCGEN05_STAGED: "tcgen05-staged", KERNEL_TCGEN05_TILE: "tcgen05-tile"}
 OK, INVALID_ARGUMENT, UNSUPPORTED, CUDA_ERROR, DEVICE_WAIT_EXPIRED, WORKSPACE_TOO_SMALL = range(6)
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libmonarch_attention_b200.so")
@@ -39,7 +40,7 @@ class Problem(C.Structure):
 
 
 class WorkspaceLayout(C.Structure):
-    _fields_ = [(n, C.c_size_t) for n in ("status", "ar", "cr", "al", "cl", "y", "total")] + \
+    _fields_ = [(n, C.c_size_t) for n in ("status", "counters", "ar", "cr", "al", "cl", "y", "total")] + \
                [("M", C.c_int32), ("kernel", C.c_int32)]
 
 

@@ -41,7 +41,7 @@ int validate(const ma_b200_problem* p, bool need_pointers) {
     return fail(MA_B200_INVALID_ARGUMENT, "unknown dtype");
   if (!(p->qk_dtype == p->v_dtype || p->v_dtype == MA_B200_F32))
     return fail(MA_B200_UNSUPPORTED, "v_dtype must equal qk_dtype or be f32");
-  if (p->kernel < MA_B200_KERNEL_AUTO || p->kernel > MA_B200_KERNEL_TCGEN05)
+  if (p->kernel < MA_B200_KERNEL_AUTO || p->kernel > MA_B200_KERNEL_TCGEN05_TILE)
     return fail(MA_B200_INVALID_ARGUMENT, "unknown kernel family");
   if ((long long)p->E * p->H > 0x7fffffffLL / 2) return fail(MA_B200_INVALID_ARGUMENT, "E*H too large");
   if (need_pointers) {
@@ -86,10 +86,10 @@ ma::Geometry make_geometry(const ma_b200_problem* p) {
 int resolve_kernel(const ma_b200_problem* p, const ma::Geometry& g, int* kernel) {
   const char* why = "";
   const bool tc_ok = ma::tc_supported(g, p->qk_dtype, p->v_dtype, &why);
-  if (p->kernel == MA_B200_KERNEL_TCGEN05 && !tc_ok)
+  if (p->kernel >= MA_B200_KERNEL_TCGEN05 && !tc_ok)
     return fail(MA_B200_UNSUPPORTED, std::string("tcgen05 path cannot run this problem: ") + why);
-  if (p->kernel == MA_B200_KERNEL_GENERIC) *kernel = MA_B200_KERNEL_GENERIC;
-  else *kernel = tc_ok ? MA_B200_KERNEL_TCGEN05 : MA_B200_KERNEL_GENERIC;
+  if (p->kernel == MA_B200_KERNEL_AUTO) *kernel = tc_ok ? MA_B200_KERNEL_TCGEN05 : MA_B200_KERNEL_GENERIC;
+  else *kernel = p->kernel;
   if (*kernel == MA_B200_KERNEL_GENERIC) {
     const size_t need = ma::generic_stage_smem_bytes(g, g.B > g.M ? ma::kStageRight : ma::kStageLeft);
     if (need > 200 * 1024)
@@ -111,6 +111,7 @@ int layout_of(const ma_b200_problem* p, ma_b200_workspace_layout* L) {
   const size_t qs = dtype_size(p->qk_dtype), vs = dtype_size(p->v_dtype);
   size_t off = 0;
   L->status = off; off = align_up(off + 256, 256);
+  L->counters = off; off = align_up(off + EH * 2 * (size_t)p->num_steps * sizeof(int), 256);
   L->ar = off;     off = align_up(off + (p->num_steps > 1 ? EH * MB * p->D * qs : 0), 256);
   L->cr = off;     off = align_up(off + (p->num_steps > 1 ? EH * MB * sizeof(float) : 0), 256);
   L->al = off;     off = align_up(off + EH * MB * p->D * qs, 256);
@@ -148,11 +149,13 @@ int run_forward(const ma_b200_problem* p, void* workspace, size_t workspace_byte
   auto cuda_fail = [&](cudaError_t e, const char* what) {
     return fail(MA_B200_CUDA_ERROR, std::string(what) + ": " + cudaGetErrorString(e));
   };
-  cudaError_t ce = cudaMemsetAsync(g.status, 0, sizeof(int), stream);
-  if (ce != cudaSuccess) return cuda_fail(ce, "cudaMemsetAsync(status)");
+  // status word and the stage-completion counters start at zero
+  cudaError_t ce = cudaMemsetAsync(ws + L.status, 0, L.ar - L.status, stream);
+  if (ce != cudaSuccess) return cuda_fail(ce, "cudaMemsetAsync(status, counters)");
+  int* counters = reinterpret_cast<int*>(ws + L.counters);
 
   ma::TcPlan* plan = nullptr;
-  if (L.kernel == MA_B200_KERNEL_TCGEN05) {
+  if (L.kernel >= MA_B200_KERNEL_TCGEN05) {
     const char* err = "";
     rc = ma::tc_plan_create(g, p->qk_dtype, &plan, &err);
     if (rc != MA_B200_OK) return fail(rc, std::string("tcgen05 plan: ") + err);
@@ -167,9 +170,11 @@ int run_forward(const ma_b200_problem* p, void* workspace, size_t workspace_byte
   }
   int stage_idx = 0;
   auto launch = [&](ma::StageKind kind, bool first) -> cudaError_t {
-    cudaError_t e = (L.kernel == MA_B200_KERNEL_TCGEN05)
-                        ? ma::launch_tc_stage(plan, g, kind, first, stream)
-                        : ma::launch_generic_stage(g, p->qk_dtype, p->v_dtype, kind, first, stream);
+    cudaError_t e;
+    if (L.kernel == MA_B200_KERNEL_TCGEN05_TILE) e = ma::launch_tc_stage(plan, g, kind, first, stream);
+    else if (L.kernel == MA_B200_KERNEL_TCGEN05_STAGED)
+      e = ma::launch_fused(plan, g, counters, stage_idx, stage_idx + 1, 0, stream);
+    else e = ma::launch_generic_stage(g, p->qk_dtype, p->v_dtype, kind, first, stream);
     ++stage_idx;
     if (ev != nullptr) cudaEventRecord(ev[stage_idx], stream);
     return e;
@@ -177,6 +182,15 @@ int run_forward(const ma_b200_problem* p, void* workspace, size_t workspace_byte
 
   rc = MA_B200_OK;
   bool first = true;
+  if (L.kernel == MA_B200_KERNEL_TCGEN05) {
+    // every stage in one persistent launch
+    ce = ma::launch_fused(plan, g, counters, 0, n_stages, 1, stream);
+    if (ce != cudaSuccess) rc = cuda_fail(ce, "fused kernel");
+    if (ev != nullptr) {
+      cudaEventRecord(ev[1], stream);
+      for (int i = 2; i <= n_stages; ++i) cudaEventRecord(ev[i], stream);
+    }
+  } else {
   for (int t = 0; t + 1 < p->num_steps && rc == MA_B200_OK; ++t) {
     if ((ce = launch(ma::kStageRight, first)) != cudaSuccess) { rc = cuda_fail(ce, "right-factor stage"); break; }
     first = false;
@@ -185,6 +199,7 @@ int run_forward(const ma_b200_problem* p, void* workspace, size_t workspace_byte
   if (rc == MA_B200_OK && (ce = launch(ma::kStageRightWithV, first)) != cudaSuccess)
     rc = cuda_fail(ce, "right-factor stage with V");
   if (rc == MA_B200_OK && (ce = launch(ma::kStageOutput, false)) != cudaSuccess) rc = cuda_fail(ce, "output stage");
+  }
 
   if (ev != nullptr) {
     if (rc == MA_B200_OK) {

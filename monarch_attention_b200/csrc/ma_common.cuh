@@ -78,5 +78,9 @@ struct TcPlan;
 int tc_plan_create(const Geometry& g, int qk_dtype, TcPlan** plan, const char** err);
 void tc_plan_destroy(TcPlan* plan);
 cudaError_t launch_tc_stage(const TcPlan* plan, const Geometry& g, StageKind kind, bool first, cudaStream_t stream);
+// Persistent fused kernel: stages [stage_begin, stage_end) of the 2T stages in one cooperative launch.
+size_t fused_counter_bytes(const Geometry& g);
+cudaError_t launch_fused(const TcPlan* plan, const Geometry& g, int* counters, int stage_begin, int stage_end,
+                         int wait_deps, cudaStream_t stream);
 
 }  // namespace ma

@@ -1,0 +1,664 @@
+// Persistent, warp-specialised tcgen05 kernel that runs every stage of the forward pass
+// in ONE launch.
+//
+// Work items are 128-row tiles: (stage, head, tile index).  Stage s of the 2T stages is
+//   right-factor (s even, s < 2T-2), left-factor (s odd, s < 2T-2),
+//   right-factor with V (s = 2T-2), output (s = 2T-1)          (reference: ma/ma_torch.py:100-105).
+// Items are laid out head-group-major: for each group of up to G heads, for each stage, for each
+// head of the group, for each tile.  CTA c of the persistent grid takes items c, c+grid, ... in
+// that order.  A stage-s item of a head may start once all 128 items of stage s-1 of that head are
+// done; completion is counted in global memory (one counter per head and stage).  Because the
+// heads of a group are interleaved, the items a stage depends on were issued (G-1)*128 items
+// earlier, so the bounded wait in the producer rarely spins, while the state of only ~G heads
+// (a few MB each) is live at a time and stays in L2: the factors never round-trip to HBM.
+// The launch is cooperative so that every CTA of the grid is resident, which the in-order
+// item schedule needs for forward progress.
+//
+// Inside a CTA (448 threads, one CTA per SM, all 512 tensor-memory columns):
+//   warp 12    TMA producer: waits for the item's dependency, loads the 2-3 operand tiles and the
+//              512-byte row vector (cr or cl) of the item into a 3-deep ring of 48 KB slots
+//   warp 13    MMA issuer: S = A B^T for item n (tcgen05.mma, fp32 accumulator S[n%2] in tensor
+//              memory), then the second contraction of item n-1 from P[(n-1)%2]
+//   warps 0-3, 4-7   two softmax groups on alternating items: tcgen05.ld of S (one row per thread),
+//              two passes (max; exp, sums, entropy), P (16-bit) to swizzled shared memory
+//   warps 8-11 epilogue: tcgen05.ld of O[n%2], scale by the row statistics, 16-byte global stores,
+//              then one release increment of the item's completion counter
+// All hand-offs are mbarriers; every wait is bounded and abortable (see ma_sm100.cuh).
+#include <cuda.h>
+
+#include <stdio.h>
+#include <stdlib.h>
+
+#include <type_traits>
+
+#include "ma_common.cuh"
+#include "ma_sm100.cuh"
+#include "ma_tc_plan.cuh"
+
+namespace ma {
+namespace {
+
+using namespace sm100;
+
+constexpr int kTile = 128;
+constexpr int kHead = 64;
+constexpr uint32_t kTileBytes = kTile * kHead * 2;  // 16 KB
+
+constexpr int kSoftmaxWarps = 8;   // two groups of four
+constexpr int kEpilogueWarp0 = 8;  // warps 8..11
+constexpr int kProducerWarp = 12;
+constexpr int kMmaWarp = 13;
+constexpr int kPublishWarp0 = 14;  // warps 14, 15
+constexpr int kThreads = 16 * 32;
+
+constexpr int kSlots = 3;
+constexpr uint32_t kSlotBytes = 3 * kTileBytes;  // A | B | V
+constexpr uint32_t kOffSlots = 0;
+constexpr uint32_t kOffP = kOffSlots + kSlots * kSlotBytes;  // 2 x 32 KB
+constexpr uint32_t kOffSv = kOffP + 2 * 2 * kTileBytes;      // 2 x 4 KB (per P buffer; left stage)
+constexpr uint32_t kOffVec = kOffSv + 2 * 4096;              // 3 x 512 B (per slot)
+constexpr uint32_t kOffStats = kOffVec + kSlots * 512;       // 4 x 128 x float4
+static_assert(kOffP % 1024 == 0 && kOffSv % 1024 == 0, "swizzled operands need 1024-byte alignment");
+constexpr uint32_t kOffBar = kOffStats + 4 * 128 * 16;
+constexpr uint32_t kSmemUsed = kOffBar + 256;
+constexpr uint32_t kSmemBytes = kSmemUsed + 1024;
+
+// mbarrier indices (8 bytes each)
+enum {
+  kBarInFull = 0,    // [3] operand slot filled by TMA
+  kBarInEmpty = 3,   // [3] operand slot released by the second contraction
+  kBarSFull = 6,     // [2] S accumulator ready
+  kBarSEmpty = 8,    // [2] S accumulator read by the softmax group
+  kBarPFull = 10,    // [2] P written
+  kBarPEmpty = 12,   // [2] P consumed by the second contraction
+  kBarOFull = 14,    // [2] O accumulator ready
+  kBarOEmpty = 16,   // [2] O accumulator read by the epilogue
+  kBarStat = 18,     // [4] row statistics written
+  kBarDone = 22,     // [4] item stored to global memory by all 128 epilogue threads
+  kBarPubFree = 26,  // [4] completion of that item published
+  kNumBars = 30
+};
+
+struct FusedArgs {
+  int stage_begin, stage_end;  // stages [begin, end) of the 2T stages run in this launch
+  int group;                   // heads interleaved per group
+  int wait_deps;               // wait on the completion counters of the previous stage
+  int* counters;               // (E*H, 2T) ints, zeroed before the first launch of a call
+  int dbg;                     // ablation switches for timing experiments (0 in production)
+};
+
+struct Item {
+  int kind, first, stage, eh, tile;
+};
+
+// Walks the items of one CTA (global indices blockIdx.x, blockIdx.x + grid, ...) without a division
+// per item: the position (group, stage, head in group, tile) is carried along.
+struct ItemCursor {
+  int gi, sl, hh, tile, gh;  // group, stage within the launch, head within the group, tile, heads in this group
+  int idx, total, stride, nst, group, EH, stage_begin, last_stage;
+
+  __device__ __forceinline__ void init(int first_idx, int stride_, const Geometry& g, const FusedArgs& a) {
+    EH = g.E * g.H;
+    nst = a.stage_end - a.stage_begin;
+    group = a.group;
+    stage_begin = a.stage_begin;
+    last_stage = 2 * g.T - 1;
+    total = (a.dbg & 32) ? 0 : nst * kTile * EH;
+    stride = stride_;
+    idx = first_idx;
+    const int per_group = nst * group * kTile;
+    gi = idx / per_group;
+    int r = idx - gi * per_group;
+    gh = min(group, EH - gi * group);
+    if (gh < 1) gh = 1;
+    sl = r / (gh * kTile);
+    r -= sl * gh * kTile;
+    hh = r / kTile;
+    tile = r - hh * kTile;
+  }
+  __device__ __forceinline__ bool valid() const { return idx < total; }
+  __device__ __forceinline__ void next() {
+    idx += stride;
+    tile += stride;
+    while (tile >= kTile) {
+      tile -= kTile;
+      if (++hh == gh) {
+        hh = 0;
+        if (++sl == nst) {
+          sl = 0;
+          ++gi;
+          gh = min(group, EH - gi * group);
+          if (gh < 1) gh = 1;
+        }
+      }
+    }
+  }
+  __device__ __forceinline__ Item get() const {
+    Item it;
+    it.tile = tile;
+    it.eh = gi * group + hh;
+    it.stage = stage_begin + sl;
+    it.kind = it.stage == last_stage
+                  ? kStageOutput
+                  : (it.stage == last_stage - 1 ? kStageRightWithV : ((it.stage & 1) ? kStageLeft : kStageRight));
+    it.first = it.stage == 0;
+    return it;
+  }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constant__ TcMaps maps, const Geometry g,
+                                                            const FusedArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bars = base + kOffBar;
+  auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + kOffBar + 8 * kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + kOffBar + 8 * kNumBars + 8);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  constexpr int kFmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+  const int total = (args.dbg & 32) ? 0 : (args.stage_end - args.stage_begin) * kTile * g.E * g.H;
+  const int nst_all = 2 * g.T;
+  long long t_begin = 0;
+  if ((args.dbg & 64) && blockIdx.x == 0) t_begin = clock64();
+
+  if (tid == 0) {
+    for (int i = 0; i < 3; ++i) { mbar_init(bar(kBarInFull + i), 1); mbar_init(bar(kBarInEmpty + i), 1); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(kBarSFull + i), 1);
+      mbar_init(bar(kBarSEmpty + i), 128);
+      mbar_init(bar(kBarPFull + i), 128);
+      mbar_init(bar(kBarPEmpty + i), 1);
+      mbar_init(bar(kBarOFull + i), 1);
+      mbar_init(bar(kBarOEmpty + i), 128);
+    }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(bar(kBarStat + i), 128);
+      mbar_init(bar(kBarDone + i), 128);
+      mbar_init(bar(kBarPubFree + i), 1);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kMmaWarp) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     base + kOffBar + 8 * kNumBars),
+                 "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  {  // zero both 16 x 128 operands that will carry 1/rowsum in their first row (left-factor stage)
+    uint32_t* z = reinterpret_cast<uint32_t*>(base_ptr + kOffSv);
+    for (int i = tid; i < 2 * 1024; i += kThreads) z[i] = 0u;
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  auto give_up = [&](int code) {
+    *abort_flag = 1;
+    atomicCAS(g.status, 0, code);
+  };
+
+  if (warp == kProducerWarp) {
+    // =========================== TMA producer ===========================================
+    if (lane == 0) {
+      int n = 0, issued = 0;
+      long long trp[14];
+      ItemCursor cur;
+      for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid(); cur.next(), ++n) {
+        const Item it = cur.get();
+        const int e = it.eh / g.H, h = it.eh - e * g.H;
+        const int slot = n % kSlots;
+        const uint32_t ph = (uint32_t)(n / kSlots) & 1u;
+        if (args.wait_deps && it.stage > 0) {
+          const int* ctr = args.counters + it.eh * nst_all + (it.stage - 1);
+          bool ready = false;
+          for (int spin = 0; spin < (1 << 24); ++spin) {
+            if (ld_acquire_gpu(ctr) >= kTile) { ready = true; break; }
+            if ((spin & 255) == 255 && *abort_flag) break;
+            __nanosleep(32);
+          }
+          if (!ready) { give_up(201); break; }
+          fence_proxy_async_all();  // the state was written with ordinary stores; the loads below are TMA
+        }
+        if (!mbar_wait_abortable(bar(kBarInEmpty + slot), ph ^ 1u, abort_flag)) { give_up(202); break; }
+        const uint32_t sA = base + kOffSlots + slot * kSlotBytes, sB = sA + kTileBytes, sV = sB + kTileBytes;
+        const uint32_t vec = base + kOffVec + slot * 512;
+        const uint32_t full = bar(kBarInFull + slot);
+        const bool right = it.kind == kStageRight || it.kind == kStageRightWithV;
+        const bool three = it.kind == kStageRightWithV || it.kind == kStageOutput;
+        const bool has_vec = !(right && it.first);
+        if ((args.dbg & 16) && n >= kSlots) {
+          mbar_arrive(full);
+          issued = n + 1;
+          continue;
+        }
+        mbar_expect_tx(full, (three ? 3u : 2u) * kTileBytes + (has_vec ? 512u : 0u));
+        if (right) {
+          if (it.first) tma_load_5d(sA, &maps.q_blk, full, 0, 0, it.tile, h, e);
+          else tma_load_5d(sA, &maps.ar_blk, full, 0, 0, it.tile, it.eh, 0);
+          tma_load_5d(sB, &maps.k_blk, full, 0, 0, it.tile, h, e);
+          if (three) tma_load_5d(sV, &maps.v_blk, full, 0, 0, it.tile, h, e);
+          if (has_vec) bulk_load(vec, g.cr + ((long long)it.eh * g.M + it.tile) * g.B, 512, full);
+        } else {
+          tma_load_5d(sA, &maps.q_col, full, 0, it.tile, 0, h, e);
+          tma_load_5d(sB, &maps.al_blk, full, 0, 0, it.tile, it.eh, 0);
+          if (three) tma_load_5d(sV, &maps.y_blk, full, 0, 0, it.tile, it.eh, 0);
+          bulk_load(vec, g.cl + ((long long)it.eh * g.B + it.tile) * g.M, 512, full);
+        }
+        issued = n + 1;
+        if ((args.dbg & 64) && blockIdx.x == 0 && n < 14) trp[n] = clock64() - t_begin;
+      }
+      if ((args.dbg & 64) && blockIdx.x == 0)
+        for (int i = 0; i < 14 && i < n; ++i) printf("producer item %d: loads issued %lld\n", i, trp[i]);
+      // Drain: make sure every copy this thread started has landed before the CTA may exit.
+      for (int m = max(0, issued - kSlots); m < issued; ++m)
+        (void)mbar_wait(bar(kBarInFull + m % kSlots), (uint32_t)(m / kSlots) & 1u);
+    }
+  } else if (warp == kMmaWarp) {
+    // =========================== MMA issuer ==============================================
+    // One thread issues every tcgen05.mma of the CTA, so its instruction count per item is on the
+    // critical path: descriptors are built once here and advanced by adding to their address field.
+    if (lane == 0) {
+      bool dead = false;
+      const uint64_t dP_k0 = smem_desc(base + kOffP, 16);                 // P as K-major A operand
+      const uint64_t dP_mn0 = smem_desc(base + kOffP, kTileBytes);         // P^T as MN-major A operand
+      const uint64_t dS0 = smem_desc(base + kOffSv, 16);                   // 16 x 128 K-major operand (1/rowsum)
+      const uint64_t dA0 = smem_desc(base + kOffSlots, 16);                // slot tile A, K-major
+      const uint64_t dBmn0 = smem_desc(base + kOffSlots + kTileBytes, kTileBytes);  // slot tile B (| V), MN-major
+      constexpr uint64_t kSlotStep = kSlotBytes >> 4, kTileStep = kTileBytes >> 4, kPStep = (2 * kTileBytes) >> 4;
+      // second contraction of local item m
+      auto second = [&](int m, int kind) {
+        const int pb = m & 1, slot = m % kSlots;
+        tc_fence_after();
+        if (!(args.dbg & 8)) {
+          const uint64_t dPk = dP_k0 + pb * kPStep, dPmn = dP_mn0 + pb * kPStep;
+          const uint64_t dB = dBmn0 + slot * kSlotStep, dV = dB + kTileStep;
+          const uint32_t tmem_o = tmem + 256 + pb * 128;
+          if (kind == kStageRight) {
+            constexpr uint32_t idesc = instr_desc(kFmt, 0, 1, kHead, kTile);
+#pragma unroll
+            for (int kk = 0; kk < kTile / 16; ++kk)
+              mma_f16(tmem_o, dPk + ((kk >> 2) * kTileStep + (kk & 3) * 2), dB + kk * 128, idesc, kk > 0);
+          } else if (kind == kStageRightWithV) {
+            constexpr uint32_t idesc = instr_desc(kFmt, 0, 1, 2 * kHead, kTile);
+#pragma unroll
+            for (int kk = 0; kk < kTile / 16; ++kk)
+              mma_f16(tmem_o, dPk + ((kk >> 2) * kTileStep + (kk & 3) * 2), dB + kk * 128, idesc, kk > 0);
+          } else if (kind == kStageLeft) {
+            constexpr uint32_t idesc_q = instr_desc(kFmt, 1, 1, kHead, kTile);
+            constexpr uint32_t idesc_s = instr_desc(kFmt, 1, 0, 16, kTile);
+            const uint64_t dS = dS0 + pb * (4096 >> 4);
+#pragma unroll
+            for (int kk = 0; kk < kTile / 16; ++kk) {
+              mma_f16(tmem_o, dPmn + kk * 128, dV + kk * 128, idesc_q, kk > 0);
+              mma_f16(tmem_o + kHead, dPmn + kk * 128, dS + ((kk >> 2) * 128 + (kk & 3) * 2), idesc_s, kk > 0);
+            }
+          } else {
+            constexpr uint32_t idesc = instr_desc(kFmt, 0, 1, kHead, kTile);
+#pragma unroll
+            for (int kk = 0; kk < kTile / 16; ++kk)
+              mma_f16(tmem_o, dPk + ((kk >> 2) * kTileStep + (kk & 3) * 2), dV + kk * 128, idesc, kk > 0);
+          }
+        }
+        mma_commit(bar(kBarOFull + pb));
+        mma_commit(bar(kBarPEmpty + pb));
+        mma_commit(bar(kBarInEmpty + slot));
+      };
+      // Issue order is data-driven: S = A B^T of item n1 runs at most one item ahead of the second
+      // contraction of item n2, and whichever has its inputs ready goes first.  (A fixed order would
+      // deadlock in the fused schedule: the operands of item n1 may depend on the completion of
+      // item n2 of this same CTA.)
+      const int cnt = (int)blockIdx.x < total ? (total - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+      int n1 = 0, n2 = 0;
+      long long tr1[14], tr2[14];
+      const bool trace = (args.dbg & 64) && blockIdx.x == 0;
+      ItemCursor cur2;  // the second contraction needs the item's kind; the first is the same for all kinds
+      cur2.init(blockIdx.x, gridDim.x, g, args);
+      long long idle = 0;
+      while (n2 < cnt && !dead) {
+        bool progressed = false;
+        if (n1 < cnt && n1 <= n2 + 1) {
+          const int slot = n1 % kSlots, sb = n1 & 1;
+          if (mbar_test(bar(kBarInFull + slot), (uint32_t)(n1 / kSlots) & 1u) &&
+              mbar_test(bar(kBarSEmpty + sb), ((uint32_t)(n1 >> 1) & 1u) ^ 1u)) {
+            tc_fence_after();
+            if (!(args.dbg & 8)) {
+              const uint64_t dA = dA0 + slot * kSlotStep, dB = dA + kTileStep;
+              constexpr uint32_t idesc1 = instr_desc(kFmt, 0, 0, kTile, kTile);
+#pragma unroll
+              for (int kk = 0; kk < kHead / 16; ++kk) mma_f16(tmem + sb * 128, dA + kk * 2, dB + kk * 2, idesc1, kk > 0);
+            }
+            mma_commit(bar(kBarSFull + sb));
+            if (trace && n1 < 14) tr1[n1] = clock64() - t_begin;
+            ++n1;
+            progressed = true;
+          }
+        }
+        if (!progressed && n2 < n1) {
+          const int pb = n2 & 1;
+          const uint32_t ph2 = (uint32_t)(n2 >> 1) & 1u;
+          if (mbar_test(bar(kBarPFull + pb), ph2) && mbar_test(bar(kBarOEmpty + pb), ph2 ^ 1u)) {
+            second(n2, cur2.get().kind);
+            if (trace && n2 < 14) tr2[n2] = clock64() - t_begin;
+            ++n2;
+            cur2.next();
+            progressed = true;
+          }
+        }
+        if (progressed) idle = 0;
+        else if (++idle > (1ll << 26) || ((idle & 1023) == 0 && *abort_flag)) { give_up(303); dead = true; }
+      }
+      if (trace) {
+        for (int i = 0; i < 14 && i < cnt; ++i) printf("mma item %d: gemm1 issued %lld gemm2 issued %lld\n", i, tr1[i], tr2[i]);
+        printf("mma done at %lld (cnt %d)\n", clock64() - t_begin, cnt);
+      }
+    }
+  } else if (warp < kSoftmaxWarps) {
+    // =========================== softmax groups ==========================================
+    const int grp = warp >> 2;                      // items with local index n = grp (mod 2)
+    const int row = (warp & 3) * 32 + lane;         // tensor-memory lane = tile row
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    int n = 0;
+    long long trs[14][3];
+    ItemCursor cur;
+    for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid(); cur.next(), ++n) {
+      if ((n & 1) != grp) continue;
+      const Item it = cur.get();
+      const int slot = n % kSlots, sb = n & 1;
+      const uint32_t ph2 = (uint32_t)(n >> 1) & 1u;
+      const bool right = it.kind == kStageRight || it.kind == kStageRightWithV;
+      const uint32_t sA = base + kOffSlots + slot * kSlotBytes, sV = sA + 2 * kTileBytes;
+      const uint32_t sP = base + kOffP + sb * 2 * kTileBytes;
+      const float* vec = reinterpret_cast<const float*>(base_ptr + kOffVec + slot * 512);
+
+      if (!mbar_wait_abortable(bar(kBarInFull + slot), (uint32_t)(n / kSlots) & 1u, abort_flag)) { give_up(401); break; }
+      if (!mbar_wait_abortable(bar(kBarSFull + sb), ph2, abort_flag)) { give_up(402); break; }
+      tc_fence_after();
+      const bool trace = (args.dbg & 64) && blockIdx.x == 0 && (tid & 127) == 0 && n < 14;
+      const long long ts0 = trace ? clock64() - t_begin : 0;
+      const uint32_t tmem_s = tmem + lane_base + sb * 128;
+
+      float row_scale = 0.f;
+      if (right) row_scale = g.sm_scale / ((it.first ? 1.0f : vec[row]) + kEps);
+
+      // Tensor-memory loads are issued one 32-column chunk ahead of the arithmetic (two register
+      // buffers), and every reduction runs on four independent accumulators, so that a warp has
+      // enough independent work in flight to keep issuing.
+      float ca[32], cb[32];
+      // ---- pass 1: row maximum -----------------------------------------------------------
+      float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+      auto max_chunk = [&](const float (&s)[32], int c) {
+        if (right) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            m0 = max3(m0, s[i], s[i + 1]);
+            m1 = max3(m1, s[i + 2], s[i + 3]);
+            m2 = max3(m2, s[i + 4], s[i + 5]);
+            m3 = max3(m3, s[i + 6], s[i + 7]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            const float4 x = *reinterpret_cast<const float4*>(vec + c * 32 + i);
+            const float4 y = *reinterpret_cast<const float4*>(vec + c * 32 + i + 4);
+            m0 = max3(m0, s[i] - x.x, s[i + 1] - x.y);
+            m1 = max3(m1, s[i + 2] - x.z, s[i + 3] - x.w);
+            m2 = max3(m2, s[i + 4] - y.x, s[i + 5] - y.y);
+            m3 = max3(m3, s[i + 6] - y.z, s[i + 7] - y.w);
+          }
+        }
+      };
+      if (args.dbg & 1) {
+        m0 = 8.0f;
+        tmem_ld32_nowait(tmem_s, ca);
+      } else {
+      tmem_ld32_nowait(tmem_s, ca);
+      tmem_wait_ld(ca); tmem_ld32_nowait(tmem_s + 32, cb); max_chunk(ca, 0);
+      tmem_wait_ld(cb); tmem_ld32_nowait(tmem_s + 64, ca); max_chunk(cb, 1);
+      tmem_wait_ld(ca); tmem_ld32_nowait(tmem_s + 96, cb); max_chunk(ca, 2);
+      tmem_wait_ld(cb); tmem_ld32_nowait(tmem_s, ca);      max_chunk(cb, 3);   // chunk 0 again, for pass 2
+      }
+      const float vmax = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+      float mul, off;
+      if (right) {
+        const float top = fmaxf(vmax * row_scale, kEps);  // lower clamp on the row maximum
+        mul = row_scale * kLog2e;
+        off = top * kLog2e;
+      } else {
+        mul = kLog2e;
+        off = vmax * kLog2e;
+      }
+      if (trace) trs[n][1] = clock64() - t_begin;
+      if (!mbar_wait_abortable(bar(kBarPEmpty + sb), ph2 ^ 1u, abort_flag)) {
+        tmem_wait_ld(ca);
+        give_up(403);
+        break;
+      }
+
+      // ---- pass 2: exponentials, sums, P -------------------------------------------------
+      float s0 = 0.f, s1 = 0.f, t0 = 0.f, t1 = 0.f;
+      auto exp_chunk = [&](const float (&s)[32], int c) {
+        uint32_t packed[16];
+        if (right) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float u0 = fmaf(s[i], mul, -off), u1 = fmaf(s[i + 1], mul, -off);
+            const float u2 = fmaf(s[i + 2], mul, -off), u3 = fmaf(s[i + 3], mul, -off);
+            const float e0 = ex2(u0), e1 = ex2(u1), e2 = ex2(u2), e3 = ex2(u3);
+            s0 += e0 + e1;
+            s1 += e2 + e3;
+            t0 = fmaf(e0, u0, fmaf(e1, u1, t0));
+            t1 = fmaf(e2, u2, fmaf(e3, u3, t1));
+            packed[i >> 1] = pack2<T>(e0, e1);
+            packed[(i >> 1) + 1] = pack2<T>(e2, e3);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float4 x = *reinterpret_cast<const float4*>(vec + c * 32 + i);
+            const float e0 = ex2(fmaf(s[i] - x.x, mul, -off)), e1 = ex2(fmaf(s[i + 1] - x.y, mul, -off));
+            const float e2 = ex2(fmaf(s[i + 2] - x.z, mul, -off)), e3 = ex2(fmaf(s[i + 3] - x.w, mul, -off));
+            s0 += e0 + e1;
+            s1 += e2 + e3;
+            packed[i >> 1] = pack2<T>(e0, e1);
+            packed[(i >> 1) + 1] = pack2<T>(e2, e3);
+          }
+        }
+        // Row `row`, columns [32c, 32c+32): K-major operand (row = M index) for the right-factor and
+        // output stages, MN-major operand holding P^T (row = K index) for the left-factor stage - the
+        // bytes land in the same place either way.
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const uint32_t col = c * 32 + q4 * 8;
+          st_shared_v4(sP + (col >> 6) * kTileBytes + swz(row, (col & 63) >> 3), packed[q4 * 4], packed[q4 * 4 + 1],
+                       packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+        }
+      };
+      if (args.dbg & 2) {
+        tmem_wait_ld(ca);
+        s0 = 1.f;
+      } else {
+      tmem_wait_ld(ca); tmem_ld32_nowait(tmem_s + 32, cb); exp_chunk(ca, 0);
+      tmem_wait_ld(cb); tmem_ld32_nowait(tmem_s + 64, ca); exp_chunk(cb, 1);
+      tmem_wait_ld(ca); tmem_ld32_nowait(tmem_s + 96, cb); exp_chunk(ca, 2);
+      tmem_wait_ld(cb);
+      }
+      // S has been read in full: hand the accumulator back before the last chunk's arithmetic
+      tc_fence_before();
+      mbar_arrive(bar(kBarSEmpty + sb));
+      if (!(args.dbg & 2)) exp_chunk(cb, 3);
+      const float row_sum = s0 + s1, row_ent = t0 + t1;
+
+
+      float4 st = make_float4(0.f, 0.f, 0.f, 0.f);  // scale of O[:, :64], scale of O[:, 64:], cl, unused
+      if (right) {
+        const float denom = row_sum + kEps;
+        st.x = g.sm_scale / denom;
+        st.y = 1.0f / denom;
+        st.z = (kLn2 * row_ent) / denom - logf(denom) * (row_sum / denom);
+      } else if (it.kind == kStageLeft) {
+        const float inv = 1.0f / row_sum;
+        st.x = 1.0f;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {  // q' = q / rowsum into the third tile of the slot
+          const uint4 v = ld_shared_v4(sA + swz(row, ch));
+          const float2 a = unpack2<T>(v.x), b = unpack2<T>(v.y), c2 = unpack2<T>(v.z), d = unpack2<T>(v.w);
+          st_shared_v4(sV + swz(row, ch), pack2<T>(a.x * inv, a.y * inv), pack2<T>(b.x * inv, b.y * inv),
+                       pack2<T>(c2.x * inv, c2.y * inv), pack2<T>(d.x * inv, d.y * inv));
+        }
+        T* srow = reinterpret_cast<T*>(base_ptr + kOffSv + sb * 4096 + (row >> 6) * 2048);
+        srow[row & 63] = Cvt<T>::from_f(inv);
+      } else {
+        st.x = 1.0f / row_sum;
+      }
+      // Row statistics for the epilogue.  The 4-deep ring cannot be overrun: item n+4 of this group
+      // needs P[(n+4)%2] free, i.e. the second contraction of item n+2, which needs O[n%2] free, i.e.
+      // the epilogue of item n finished.
+      *reinterpret_cast<float4*>(base_ptr + kOffStats + ((n & 3) * 128 + row) * 16) = st;
+      mbar_arrive(bar(kBarStat + (n & 3)));
+      fence_async_smem();
+      mbar_arrive(bar(kBarPFull + sb));
+      if (trace) { trs[n][0] = ts0; trs[n][2] = clock64() - t_begin; }
+    }
+    if ((args.dbg & 64) && blockIdx.x == 0 && (tid & 127) == 0)
+      for (int i = grp; i < 14 && i < n; i += 2)
+        printf("softmax item %d: S ready %lld  max done %lld  P done %lld\n", i, trs[i][0], trs[i][1], trs[i][2]);
+  } else if (warp < kProducerWarp) {
+    // =========================== epilogue group =============================================
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    int n = 0;
+    long long tre[14][2];
+    ItemCursor cur;
+    for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid(); cur.next(), ++n) {
+      const Item it = cur.get();
+      const int ob = n & 1;
+      if (!mbar_wait_abortable(bar(kBarStat + (n & 3)), (uint32_t)(n >> 2) & 1u, abort_flag) ||
+          !mbar_wait_abortable(bar(kBarOFull + ob), (uint32_t)(n >> 1) & 1u, abort_flag)) {
+        give_up(501);
+        break;
+      }
+      tc_fence_after();
+      const bool trace = (args.dbg & 64) && blockIdx.x == 0 && row == 0 && n < 14;
+      const long long te0 = trace ? clock64() - t_begin : 0;
+      const float4 st = *reinterpret_cast<const float4*>(base_ptr + kOffStats + ((n & 3) * 128 + row) * 16);
+      const uint32_t tmem_o = tmem + lane_base + 256 + ob * 128;
+      T* dst0;
+      if (it.kind == kStageRight || it.kind == kStageRightWithV) {
+        dst0 = reinterpret_cast<T*>(g.al) + (((long long)it.eh * g.B + row) * g.M + it.tile) * kHead;
+        g.cl[((long long)it.eh * g.B + row) * g.M + it.tile] = st.z;
+      } else if (it.kind == kStageLeft) {
+        dst0 = reinterpret_cast<T*>(g.ar) + (((long long)it.eh * g.M + row) * g.B + it.tile) * kHead;
+      } else {
+        const int e = it.eh / g.H, h = it.eh - e * g.H;
+        dst0 = reinterpret_cast<T*>(const_cast<void*>(g.out.ptr)) + (long long)e * g.out.se + (long long)h * g.out.sh +
+               ((long long)row * g.B + it.tile) * g.out.sn;
+      }
+      // 64 accumulator columns -> one 128-byte row: both chunk loads in flight, then 8 x 16-byte stores
+      auto store_row = [&](T* dst, uint32_t taddr, float scale) {
+        float o0[32], o1[32];
+        tmem_ld32_nowait(taddr, o0);
+        tmem_ld32_nowait(taddr + 32, o1);
+        tmem_wait_ld(o0);
+        tmem_wait_ld(o1);
+#pragma unroll
+        for (int h8 = 0; h8 < 4; ++h8) {  // 32-byte stores: every touched sector is written whole
+          const float* p = (h8 < 2 ? o0 : o1) + (h8 & 1) * 16;
+          uint32_t w[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) w[i] = pack2<T>(p[2 * i] * scale, p[2 * i + 1] * scale);
+          st_global_v8(dst + h8 * 16, w);
+        }
+      };
+      if (!(args.dbg & 4)) store_row(dst0, tmem_o, st.x);
+      if (args.dbg & 4) {
+      } else if (it.kind == kStageRightWithV) {
+        store_row(reinterpret_cast<T*>(g.y) + (((long long)it.eh * g.B + row) * g.M + it.tile) * kHead, tmem_o + kHead,
+                  st.y);
+      } else if (it.kind == kStageLeft) {
+        float o[32];
+        tmem_ld32(tmem_o + kHead, o);
+        g.cr[((long long)it.eh * g.M + row) * g.B + it.tile] = o[0];
+      }
+      tc_fence_before();
+      mbar_arrive(bar(kBarOEmpty + ob));
+      if (trace) { tre[n][0] = te0; tre[n][1] = clock64() - t_begin; }
+      if (args.wait_deps) {
+        // hand the item to a publisher warp (4-deep ring), which makes the stores visible device-wide
+        // and counts the item as complete without holding this group up
+        if (!mbar_wait_abortable(bar(kBarPubFree + (n & 3)), ((uint32_t)(n >> 2) & 1u) ^ 1u, abort_flag)) {
+          give_up(502);
+          break;
+        }
+        mbar_arrive(bar(kBarDone + (n & 3)));
+      }
+    }
+    if ((args.dbg & 64) && blockIdx.x == 0 && row == 0)
+      for (int i = 0; i < 14 && i < n; ++i) printf("epilogue item %d: O ready %lld  stored %lld\n", i, tre[i][0], tre[i][1]);
+  } else if (warp >= kPublishWarp0) {
+    // =========================== publishers ===================================================
+    if (lane == 0 && args.wait_deps) {
+      const int par = warp - kPublishWarp0;
+      int n = 0;
+      ItemCursor cur;
+      for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid(); cur.next(), ++n) {
+        if ((n & 1) != par) continue;
+        const Item it = cur.get();
+        if (!mbar_wait_abortable(bar(kBarDone + (n & 3)), (uint32_t)(n >> 2) & 1u, abort_flag)) { give_up(601); break; }
+        if (it.stage != nst_all - 1) {  // nothing consumes the output stage
+          __threadfence();
+          atomicAdd(args.counters + it.eh * nst_all + it.stage, 1);
+        }
+        mbar_arrive(bar(kBarPubFree + (n & 3)));
+      }
+    }
+  }
+
+  // ---- teardown ------------------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if ((args.dbg & 64) && blockIdx.x == 0 && tid == 0) printf("cta 0 all roles done at %lld\n", clock64() - t_begin);
+  if (warp == kMmaWarp) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+  }
+}
+
+}  // namespace
+
+size_t fused_counter_bytes(const Geometry& g) { return (size_t)g.E * g.H * 2 * g.T * sizeof(int); }
+
+// Runs stages [stage_begin, stage_end) in one cooperative launch.
+cudaError_t launch_fused(const TcPlan* plan, const Geometry& g, int* counters, int stage_begin, int stage_end,
+                         int wait_deps, cudaStream_t stream) {
+  int dev = 0, sms = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return e;
+  FusedArgs a;
+  a.stage_begin = stage_begin;
+  a.stage_end = stage_end;
+  a.group = g.E * g.H < 4 ? g.E * g.H : 4;
+  a.wait_deps = wait_deps;
+  a.counters = counters;
+  {
+    const char* d = getenv("MA_B200_DEBUG");
+    a.dbg = d ? atoi(d) : 0;
+  }
+  const int total = (stage_end - stage_begin) * kTile * g.E * g.H;
+  const int grid = total < sms ? total : sms;
+  const void* fn = plan->qk_dtype == MA_B200_BF16 ? (const void*)fused_kernel<__nv_bfloat16>
+                                                  : (const void*)fused_kernel<__half>;
+  e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+  if (e != cudaSuccess) return e;
+  void* params[] = {(void*)&plan->maps, (void*)&g, (void*)&a};
+  return cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kThreads), params, kSmemBytes, stream);
+}
+
+}  // namespace ma

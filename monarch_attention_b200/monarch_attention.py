@@ -150,13 +150,19 @@ def register_impl(name: str, fn: MonarchAttentionFn) -> None:
 register_impl("b200", monarch_attention_b200)
 register_impl("b200-generic", _generic)
 register_impl("b200-tcgen05", _tcgen05)
+register_impl("b200-tcgen05-staged",
+              lambda q, k, v, m, T, B, pp: monarch_attention_b200(q, k, v, m, T, B, pp, kernel=_cabi.KERNEL_TCGEN05_STAGED))
+register_impl("b200-tcgen05-tile",
+              lambda q, k, v, m, T, B, pp: monarch_attention_b200(q, k, v, m, T, B, pp, kernel=_cabi.KERNEL_TCGEN05_TILE))
 
 
 class MonarchAttention(nn.Module):
     """Drop-in for the reference module (reference: ma/monarch_attention.py:37-66).
 
-    ``impl`` selects the kernel family: "b200" (default: tensor-core path when the problem
-    fits it, otherwise the generic path), "b200-generic" or "b200-tcgen05".  The reference's
+    ``impl`` selects the kernel family: "b200" (default: fused tensor-core kernel when the
+    problem fits it, otherwise the generic path), "b200-generic", "b200-tcgen05" (fused, one
+    launch), "b200-tcgen05-staged" (same kernel, one launch per stage) or "b200-tcgen05-tile"
+    (one tile per CTA).  The reference's
     "torch" and "triton" implementations are not part of this library; asking for an
     unknown name raises ``ValueError`` exactly as the reference does.
     """

@@ -44,10 +44,14 @@ def test_generic_kernels_match_oracle_and_golden(ma, case):
 TC_CASES = [c for c in CASES if c["B"] == 128 and c["N"] == 16384 and c["dtype"] in ("bf16", "f16")]
 
 
+TC_IMPLS = ["b200-tcgen05", "b200-tcgen05-staged", "b200-tcgen05-tile"]
+
+
+@pytest.mark.parametrize("impl", TC_IMPLS)
 @pytest.mark.parametrize("case", TC_CASES, ids=[c["name"] for c in TC_CASES])
-def test_tcgen05_kernels_match_oracle_and_golden(ma, case):
+def test_tcgen05_kernels_match_oracle_and_golden(ma, case, impl):
     q, k, v, mask = make_inputs(case)
-    out = _run(ma, case, "b200-tcgen05", q, k, v, mask)
+    out = _run(ma, case, impl, q, k, v, mask)
     ref = monarch_attention_oracle(q, k, v, mask, case["T"], case["B"], case["pre_pad"])
     vd = case["vdtype"]
     check_close(out.double().cpu().numpy(), ref.double().numpy(), vd, case["name"] + " vs oracle")
@@ -83,7 +87,8 @@ def _state_from_workspace(ma, q, k, v, T, B, kernel):
     return out, st, L
 
 
-@pytest.mark.parametrize("name,kernel", [("cfg3_n16384_unit_bf16", 2), ("cfg3_n16384_unit_bf16", 1),
+@pytest.mark.parametrize("name,kernel", [("cfg3_n16384_unit_bf16", 2), ("cfg3_n16384_unit_bf16", 3),
+                                         ("cfg3_n16384_unit_bf16", 4), ("cfg3_n16384_unit_bf16", 1),
                                          ("cfg3_n4096_unit_bf16", 1), ("edge_t4_f32", 1)])
 def test_stage_state_matches_oracle(ma, name, kernel):
     """Every stage-to-stage tensor (ar, cr, al, cl, y), not just the final output."""
@@ -160,7 +165,7 @@ def full_inputs():
     return tuple(t.to(torch.bfloat16).to(dev) for t in (q, k, v))
 
 
-@pytest.mark.parametrize("impl", ["b200-tcgen05", "b200-generic"])
+@pytest.mark.parametrize("impl", TC_IMPLS + ["b200-generic"])
 def test_full_size_constant_value_rows(ma, full_inputs, impl):
     """The Monarch matrix is row-stochastic: with every row of V equal to c, every output row is c."""
     q, k, _ = full_inputs
@@ -178,6 +183,11 @@ def test_full_size_paths_agree_and_heads_permute(ma, full_inputs):
     a = mod_tc(q, k, v)
     b = mod_gen(q, k, v)
     check_close(a.double().cpu().numpy(), b.double().cpu().numpy(), "bf16", "tcgen05 vs generic, full size")
+    for other in ("b200-tcgen05-staged", "b200-tcgen05-tile"):
+        c = ma.MonarchAttention(128, 2, "post", impl=other)(q, k, v)
+        check_close(c.double().cpu().numpy(), a.double().cpu().numpy(), "bf16", f"{other} vs fused, full size")
+    for _ in range(3):   # the fused schedule must be deterministic run to run
+        assert torch.equal(mod_tc(q, k, v), a)
     perm = torch.randperm(16, device=q.device)
     a_p = mod_tc(q[:, perm], k[:, perm], v[:, perm])   # strided head views
     assert torch.equal(a[:, perm], a_p)
