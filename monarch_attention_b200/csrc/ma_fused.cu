@@ -14,15 +14,19 @@
 // The launch is cooperative so that every CTA of the grid is resident, which the in-order
 // item schedule needs for forward progress.
 //
-// Inside a CTA (448 threads, one CTA per SM, all 512 tensor-memory columns):
+// Inside a CTA (512 threads, one CTA per SM, all 512 tensor-memory columns):
+//   warps 0-3, 4-7   two softmax groups on alternating items, one tile row per thread: the whole row
+//              of S is read into registers in one tcgen05.ld round trip (raised register budget via
+//              setmaxnreg), two passes over the registers (max; exp, sums, entropy), P (16-bit) to
+//              swizzled shared memory, row statistics to a small ring for the epilogue
+//   warps 8-11 epilogue group: waits for O[n%2], scales it by the row statistics and stores rows to
+//              global memory with 32-byte stores (it absorbs the latency of the second contraction so
+//              that the softmax groups never wait for it)
 //   warp 12    TMA producer: waits for the item's dependency, loads the 2-3 operand tiles and the
 //              512-byte row vector (cr or cl) of the item into a 3-deep ring of 48 KB slots
-//   warp 13    MMA issuer: S = A B^T for item n (tcgen05.mma, fp32 accumulator S[n%2] in tensor
-//              memory), then the second contraction of item n-1 from P[(n-1)%2]
-//   warps 0-3, 4-7   two softmax groups on alternating items: tcgen05.ld of S (one row per thread),
-//              two passes (max; exp, sums, entropy), P (16-bit) to swizzled shared memory
-//   warps 8-11 epilogue: tcgen05.ld of O[n%2], scale by the row statistics, 16-byte global stores,
-//              then one release increment of the item's completion counter
+//   warp 13    MMA issuer 1: S = A B^T for item n (tcgen05.mma, fp32 accumulator S[n%2] in tensor memory)
+//   warp 14    MMA issuer 2: the second contraction of item n from P[n%2] into O[n%2]
+//   warp 15    publisher: device-scope fence and one increment of the item's completion counter
 // All hand-offs are mbarriers; every wait is bounded and abortable (see ma_sm100.cuh).
 #include <cuda.h>
 
@@ -44,11 +48,12 @@ constexpr int kTile = 128;
 constexpr int kHead = 64;
 constexpr uint32_t kTileBytes = kTile * kHead * 2;  // 16 KB
 
-constexpr int kSoftmaxWarps = 8;   // two groups of four
-constexpr int kEpilogueWarp0 = 8;  // warps 8..11
+constexpr int kSoftmaxWarps = 8;    // two groups of four
+constexpr int kEpilogueWarp0 = 8;   // warps 8..11
 constexpr int kProducerWarp = 12;
-constexpr int kMmaWarp = 13;
-constexpr int kPublishWarp0 = 14;  // warps 14, 15
+constexpr int kMma1Warp = 13;
+constexpr int kMma2Warp = 14;
+constexpr int kPublishWarp = 15;
 constexpr int kThreads = 16 * 32;
 
 constexpr int kSlots = 3;
@@ -57,8 +62,8 @@ constexpr uint32_t kOffSlots = 0;
 constexpr uint32_t kOffP = kOffSlots + kSlots * kSlotBytes;  // 2 x 32 KB
 constexpr uint32_t kOffSv = kOffP + 2 * 2 * kTileBytes;      // 2 x 4 KB (per P buffer; left stage)
 constexpr uint32_t kOffVec = kOffSv + 2 * 4096;              // 3 x 512 B (per slot)
-constexpr uint32_t kOffStats = kOffVec + kSlots * 512;       // 4 x 128 x float4
 static_assert(kOffP % 1024 == 0 && kOffSv % 1024 == 0, "swizzled operands need 1024-byte alignment");
+constexpr uint32_t kOffStats = kOffVec + kSlots * 512;       // 4 x 128 x float4 row statistics
 constexpr uint32_t kOffBar = kOffStats + 4 * 128 * 16;
 constexpr uint32_t kSmemUsed = kOffBar + 256;
 constexpr uint32_t kSmemBytes = kSmemUsed + 1024;
@@ -72,10 +77,10 @@ enum {
   kBarPFull = 10,    // [2] P written
   kBarPEmpty = 12,   // [2] P consumed by the second contraction
   kBarOFull = 14,    // [2] O accumulator ready
-  kBarOEmpty = 16,   // [2] O accumulator read by the epilogue
-  kBarStat = 18,     // [4] row statistics written
-  kBarDone = 22,     // [4] item stored to global memory by all 128 epilogue threads
-  kBarPubFree = 26,  // [4] completion of that item published
+  kBarOEmpty = 16,   // [2] O accumulator read by the epilogue group
+  kBarDone = 18,     // [4] item stored to global memory by all 128 epilogue threads
+  kBarPubFree = 22,  // [4] completion of that item published
+  kBarStat = 26,     // [4] row statistics of the item written by its softmax group
   kNumBars = 30
 };
 
@@ -84,7 +89,7 @@ struct FusedArgs {
   int group;                   // heads interleaved per group
   int wait_deps;               // wait on the completion counters of the previous stage
   int* counters;               // (E*H, 2T) ints, zeroed before the first launch of a call
-  int dbg;                     // ablation switches for timing experiments (0 in production)
+  int dbg;                     // ablation switches, read only by diagnostic builds (-DMA_DIAG)
 };
 
 struct Item {
@@ -103,7 +108,11 @@ struct ItemCursor {
     group = a.group;
     stage_begin = a.stage_begin;
     last_stage = 2 * g.T - 1;
+#ifdef MA_DIAG
     total = (a.dbg & 32) ? 0 : nst * kTile * EH;
+#else
+    total = nst * kTile * EH;
+#endif
     stride = stride_;
     idx = first_idx;
     const int per_group = nst * group * kTile;
@@ -158,11 +167,15 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + kOffBar + 8 * kNumBars + 8);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef MA_DIAG
+  const int dbg_flags = args.dbg;  // ablation switches for timing experiments (diagnostic builds only)
+#else
+  constexpr int dbg_flags = 0;
+#endif
   constexpr int kFmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
-  const int total = (args.dbg & 32) ? 0 : (args.stage_end - args.stage_begin) * kTile * g.E * g.H;
+  const int total = (dbg_flags & 32) ? 0 : (args.stage_end - args.stage_begin) * kTile * g.E * g.H;
   const int nst_all = 2 * g.T;
-  long long t_begin = 0;
-  if ((args.dbg & 64) && blockIdx.x == 0) t_begin = clock64();
+
 
   if (tid == 0) {
     for (int i = 0; i < 3; ++i) { mbar_init(bar(kBarInFull + i), 1); mbar_init(bar(kBarInEmpty + i), 1); }
@@ -175,14 +188,14 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       mbar_init(bar(kBarOEmpty + i), 128);
     }
     for (int i = 0; i < 4; ++i) {
-      mbar_init(bar(kBarStat + i), 128);
       mbar_init(bar(kBarDone + i), 128);
+      mbar_init(bar(kBarStat + i), 128);
       mbar_init(bar(kBarPubFree + i), 1);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == kMmaWarp) {
+  if (warp == kMma1Warp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      base + kOffBar + 8 * kNumBars),
                  "r"(512)
@@ -204,11 +217,15 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
     atomicCAS(g.status, 0, code);
   };
 
+  // Register budget per warpgroup (the launch gives every thread 128): the two softmax groups hold a
+  // whole accumulator row each, the epilogue group half a row, the single-thread roles little.
+  // 256 x 192 + 128 x 80 + 128 x 48 = 65536 = 512 x 128, so the increase can always be granted.
+  if (warp >= kProducerWarp) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
   if (warp == kProducerWarp) {
     // =========================== TMA producer ===========================================
     if (lane == 0) {
       int n = 0, issued = 0;
-      long long trp[14];
       ItemCursor cur;
       for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid(); cur.next(), ++n) {
         const Item it = cur.get();
@@ -233,7 +250,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         const bool right = it.kind == kStageRight || it.kind == kStageRightWithV;
         const bool three = it.kind == kStageRightWithV || it.kind == kStageOutput;
         const bool has_vec = !(right && it.first);
-        if ((args.dbg & 16) && n >= kSlots) {
+        if ((dbg_flags & 16) && n >= kSlots) {
           mbar_arrive(full);
           issued = n + 1;
           continue;
@@ -252,124 +269,195 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           bulk_load(vec, g.cl + ((long long)it.eh * g.B + it.tile) * g.M, 512, full);
         }
         issued = n + 1;
-        if ((args.dbg & 64) && blockIdx.x == 0 && n < 14) trp[n] = clock64() - t_begin;
       }
-      if ((args.dbg & 64) && blockIdx.x == 0)
-        for (int i = 0; i < 14 && i < n; ++i) printf("producer item %d: loads issued %lld\n", i, trp[i]);
       // Drain: make sure every copy this thread started has landed before the CTA may exit.
       for (int m = max(0, issued - kSlots); m < issued; ++m)
         (void)mbar_wait(bar(kBarInFull + m % kSlots), (uint32_t)(m / kSlots) & 1u);
     }
-  } else if (warp == kMmaWarp) {
-    // =========================== MMA issuer ==============================================
-    // One thread issues every tcgen05.mma of the CTA, so its instruction count per item is on the
-    // critical path: descriptors are built once here and advanced by adding to their address field.
+  } else if (warp == kMma1Warp) {
+    // =========================== MMA issuer 1: S = A B^T ====================================
+    // Two single-thread issuers with blocking waits (a polling issuer would take issue slots from the
+    // softmax warps that share its scheduler).  They are independent on purpose: the operands of item
+    // n+1 may depend on the completion of item n of this same CTA, so the second contraction of item n
+    // must never queue behind a wait for item n+1.
     if (lane == 0) {
-      bool dead = false;
-      const uint64_t dP_k0 = smem_desc(base + kOffP, 16);                 // P as K-major A operand
-      const uint64_t dP_mn0 = smem_desc(base + kOffP, kTileBytes);         // P^T as MN-major A operand
-      const uint64_t dS0 = smem_desc(base + kOffSv, 16);                   // 16 x 128 K-major operand (1/rowsum)
-      const uint64_t dA0 = smem_desc(base + kOffSlots, 16);                // slot tile A, K-major
-      const uint64_t dBmn0 = smem_desc(base + kOffSlots + kTileBytes, kTileBytes);  // slot tile B (| V), MN-major
-      constexpr uint64_t kSlotStep = kSlotBytes >> 4, kTileStep = kTileBytes >> 4, kPStep = (2 * kTileBytes) >> 4;
-      // second contraction of local item m
-      auto second = [&](int m, int kind) {
-        const int pb = m & 1, slot = m % kSlots;
+      const uint32_t dA0 = smem_desc_lo(base + kOffSlots, 16);  // slot tile A, K-major; tile B follows it
+      constexpr uint32_t kSlotStep = kSlotBytes >> 4, kTileStep = kTileBytes >> 4;
+      constexpr uint32_t idesc1 = instr_desc(kFmt, 0, 0, kTile, kTile);
+      int n = 0;
+      for (int idx = blockIdx.x; idx < total; idx += gridDim.x, ++n) {
+        const int slot = n % kSlots, sb = n & 1;
+        if (!mbar_wait_abortable(bar(kBarInFull + slot), (uint32_t)(n / kSlots) & 1u, abort_flag)) { give_up(301); break; }
+        if (!mbar_wait_abortable(bar(kBarSEmpty + sb), ((uint32_t)(n >> 1) & 1u) ^ 1u, abort_flag)) { give_up(302); break; }
         tc_fence_after();
-        if (!(args.dbg & 8)) {
-          const uint64_t dPk = dP_k0 + pb * kPStep, dPmn = dP_mn0 + pb * kPStep;
-          const uint64_t dB = dBmn0 + slot * kSlotStep, dV = dB + kTileStep;
+        if (!(dbg_flags & 8)) {
+          const uint32_t dA = dA0 + slot * kSlotStep, dB = dA + kTileStep;
+#pragma unroll
+          for (int kk = 0; kk < kHead / 16; ++kk) mma_f16_lo(tmem + sb * 128, dA + kk * 2, dB + kk * 2, idesc1, kk > 0);
+        }
+        mma_commit(bar(kBarSFull + sb));
+      }
+    }
+  } else if (warp == kMma2Warp) {
+    // =========================== MMA issuer 2: O = P [B | V] =================================
+    if (lane == 0) {
+      const uint32_t dP_k0 = smem_desc_lo(base + kOffP, 16);           // P as K-major A operand
+      const uint32_t dP_mn0 = smem_desc_lo(base + kOffP, kTileBytes);   // P^T as MN-major A operand
+      const uint32_t dS0 = smem_desc_lo(base + kOffSv, 16);             // 16 x 128 K-major operand (1/rowsum)
+      const uint32_t dBmn0 = smem_desc_lo(base + kOffSlots + kTileBytes, kTileBytes);  // slot tile B (| V), MN-major
+      constexpr uint32_t kSlotStep = kSlotBytes >> 4, kTileStep = kTileBytes >> 4, kPStep = (2 * kTileBytes) >> 4;
+      int n = 0;
+      ItemCursor cur;
+      for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid(); cur.next(), ++n) {
+        const int kind = cur.get().kind;
+        const int pb = n & 1, slot = n % kSlots;
+        const uint32_t ph2 = (uint32_t)(n >> 1) & 1u;
+        if (!mbar_wait_abortable(bar(kBarPFull + pb), ph2, abort_flag)) { give_up(303); break; }
+        if (!mbar_wait_abortable(bar(kBarOEmpty + pb), ph2 ^ 1u, abort_flag)) { give_up(304); break; }
+        tc_fence_after();
+        if (!(dbg_flags & 8)) {
+          const uint32_t dPk = dP_k0 + pb * kPStep, dPmn = dP_mn0 + pb * kPStep;
+          const uint32_t dB = dBmn0 + slot * kSlotStep, dV = dB + kTileStep;
           const uint32_t tmem_o = tmem + 256 + pb * 128;
           if (kind == kStageRight) {
             constexpr uint32_t idesc = instr_desc(kFmt, 0, 1, kHead, kTile);
 #pragma unroll
             for (int kk = 0; kk < kTile / 16; ++kk)
-              mma_f16(tmem_o, dPk + ((kk >> 2) * kTileStep + (kk & 3) * 2), dB + kk * 128, idesc, kk > 0);
+              mma_f16_lo(tmem_o, dPk + ((kk >> 2) * kTileStep + (kk & 3) * 2), dB + kk * 128, idesc, kk > 0);
           } else if (kind == kStageRightWithV) {
+            // the V tile follows the B tile in the slot: second 64-column atom of a 128-wide operand
             constexpr uint32_t idesc = instr_desc(kFmt, 0, 1, 2 * kHead, kTile);
 #pragma unroll
             for (int kk = 0; kk < kTile / 16; ++kk)
-              mma_f16(tmem_o, dPk + ((kk >> 2) * kTileStep + (kk & 3) * 2), dB + kk * 128, idesc, kk > 0);
+              mma_f16_lo(tmem_o, dPk + ((kk >> 2) * kTileStep + (kk & 3) * 2), dB + kk * 128, idesc, kk > 0);
           } else if (kind == kStageLeft) {
             constexpr uint32_t idesc_q = instr_desc(kFmt, 1, 1, kHead, kTile);
             constexpr uint32_t idesc_s = instr_desc(kFmt, 1, 0, 16, kTile);
-            const uint64_t dS = dS0 + pb * (4096 >> 4);
+            const uint32_t dS = dS0 + pb * (4096 >> 4);
 #pragma unroll
             for (int kk = 0; kk < kTile / 16; ++kk) {
-              mma_f16(tmem_o, dPmn + kk * 128, dV + kk * 128, idesc_q, kk > 0);
-              mma_f16(tmem_o + kHead, dPmn + kk * 128, dS + ((kk >> 2) * 128 + (kk & 3) * 2), idesc_s, kk > 0);
+              mma_f16_lo(tmem_o, dPmn + kk * 128, dV + kk * 128, idesc_q, kk > 0);
+              mma_f16_lo(tmem_o + kHead, dPmn + kk * 128, dS + ((kk >> 2) * 128 + (kk & 3) * 2), idesc_s, kk > 0);
             }
           } else {
             constexpr uint32_t idesc = instr_desc(kFmt, 0, 1, kHead, kTile);
 #pragma unroll
             for (int kk = 0; kk < kTile / 16; ++kk)
-              mma_f16(tmem_o, dPk + ((kk >> 2) * kTileStep + (kk & 3) * 2), dV + kk * 128, idesc, kk > 0);
+              mma_f16_lo(tmem_o, dPk + ((kk >> 2) * kTileStep + (kk & 3) * 2), dV + kk * 128, idesc, kk > 0);
           }
         }
         mma_commit(bar(kBarOFull + pb));
         mma_commit(bar(kBarPEmpty + pb));
         mma_commit(bar(kBarInEmpty + slot));
-      };
-      // Issue order is data-driven: S = A B^T of item n1 runs at most one item ahead of the second
-      // contraction of item n2, and whichever has its inputs ready goes first.  (A fixed order would
-      // deadlock in the fused schedule: the operands of item n1 may depend on the completion of
-      // item n2 of this same CTA.)
-      const int cnt = (int)blockIdx.x < total ? (total - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-      int n1 = 0, n2 = 0;
-      long long tr1[14], tr2[14];
-      const bool trace = (args.dbg & 64) && blockIdx.x == 0;
-      ItemCursor cur2;  // the second contraction needs the item's kind; the first is the same for all kinds
-      cur2.init(blockIdx.x, gridDim.x, g, args);
-      long long idle = 0;
-      while (n2 < cnt && !dead) {
-        bool progressed = false;
-        if (n1 < cnt && n1 <= n2 + 1) {
-          const int slot = n1 % kSlots, sb = n1 & 1;
-          if (mbar_test(bar(kBarInFull + slot), (uint32_t)(n1 / kSlots) & 1u) &&
-              mbar_test(bar(kBarSEmpty + sb), ((uint32_t)(n1 >> 1) & 1u) ^ 1u)) {
-            tc_fence_after();
-            if (!(args.dbg & 8)) {
-              const uint64_t dA = dA0 + slot * kSlotStep, dB = dA + kTileStep;
-              constexpr uint32_t idesc1 = instr_desc(kFmt, 0, 0, kTile, kTile);
-#pragma unroll
-              for (int kk = 0; kk < kHead / 16; ++kk) mma_f16(tmem + sb * 128, dA + kk * 2, dB + kk * 2, idesc1, kk > 0);
-            }
-            mma_commit(bar(kBarSFull + sb));
-            if (trace && n1 < 14) tr1[n1] = clock64() - t_begin;
-            ++n1;
-            progressed = true;
-          }
-        }
-        if (!progressed && n2 < n1) {
-          const int pb = n2 & 1;
-          const uint32_t ph2 = (uint32_t)(n2 >> 1) & 1u;
-          if (mbar_test(bar(kBarPFull + pb), ph2) && mbar_test(bar(kBarOEmpty + pb), ph2 ^ 1u)) {
-            second(n2, cur2.get().kind);
-            if (trace && n2 < 14) tr2[n2] = clock64() - t_begin;
-            ++n2;
-            cur2.next();
-            progressed = true;
-          }
-        }
-        if (progressed) idle = 0;
-        else if (++idle > (1ll << 26) || ((idle & 1023) == 0 && *abort_flag)) { give_up(303); dead = true; }
-      }
-      if (trace) {
-        for (int i = 0; i < 14 && i < cnt; ++i) printf("mma item %d: gemm1 issued %lld gemm2 issued %lld\n", i, tr1[i], tr2[i]);
-        printf("mma done at %lld (cnt %d)\n", clock64() - t_begin, cnt);
       }
     }
-  } else if (warp < kSoftmaxWarps) {
+  } else {
+    // =========================== publisher =====================================================
+    // Makes the stores of every finished item visible device-wide and counts the item in its
+    // (head, stage) completion counter, off the critical path of the epilogue group.
+    if (lane == 0 && args.wait_deps) {
+      int n = 0;
+      ItemCursor cur;
+      for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid(); cur.next(), ++n) {
+        const Item it = cur.get();
+        if (!mbar_wait_abortable(bar(kBarDone + (n & 3)), (uint32_t)(n >> 2) & 1u, abort_flag)) { give_up(601); break; }
+        if (it.stage != nst_all - 1) {  // nothing consumes the output stage
+          __threadfence();
+          atomicAdd(args.counters + it.eh * nst_all + it.stage, 1);
+        }
+        mbar_arrive(bar(kBarPubFree + (n & 3)));
+      }
+    }
+  }
+  } else if (warp >= kEpilogueWarp0) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
+    // =========================== epilogue group =================================================
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    int n = 0;
+    ItemCursor cur;
+    for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid(); cur.next(), ++n) {
+      const Item it = cur.get();
+      const int ob = n & 1;
+      if (!mbar_wait_abortable(bar(kBarStat + (n & 3)), (uint32_t)(n >> 2) & 1u, abort_flag) ||
+          !mbar_wait_abortable(bar(kBarOFull + ob), (uint32_t)(n >> 1) & 1u, abort_flag)) {
+        give_up(501);
+        break;
+      }
+      tc_fence_after();
+      const float4 st = *reinterpret_cast<const float4*>(base_ptr + kOffStats + ((n & 3) * 128 + row) * 16);
+      const uint32_t tmem_o = tmem + lane_base + 256 + ob * 128;
+      T* dst0;
+      if (it.kind == kStageRight || it.kind == kStageRightWithV) {
+        dst0 = reinterpret_cast<T*>(g.al) + (((long long)it.eh * g.B + row) * g.M + it.tile) * kHead;
+        g.cl[((long long)it.eh * g.B + row) * g.M + it.tile] = st.z;
+      } else if (it.kind == kStageLeft) {
+        dst0 = reinterpret_cast<T*>(g.ar) + (((long long)it.eh * g.M + row) * g.B + it.tile) * kHead;
+      } else {
+        const int e = it.eh / g.H, h = it.eh - e * g.H;
+        dst0 = reinterpret_cast<T*>(const_cast<void*>(g.out.ptr)) + (long long)e * g.out.se + (long long)h * g.out.sh +
+               ((long long)row * g.B + it.tile) * g.out.sn;
+      }
+      // 64 accumulator columns -> one 128-byte row: both chunk loads in flight, then 4 x 32-byte stores
+      // (every touched sector is written whole)
+      auto store_row = [&](T* dst, uint32_t taddr, float scale) {
+        float o0[32], o1[32];
+        tmem_ld32_nowait(taddr, o0);
+        tmem_ld32_nowait(taddr + 32, o1);
+        tmem_wait_ld(o0);
+        tmem_wait_ld(o1);
+#pragma unroll
+        for (int h8 = 0; h8 < 4; ++h8) {
+          const float* p = (h8 < 2 ? o0 : o1) + (h8 & 1) * 16;
+          uint32_t w[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) w[i] = pack2<T>(p[2 * i] * scale, p[2 * i + 1] * scale);
+          st_global_v8(dst + h8 * 16, w);
+        }
+      };
+      if (!(dbg_flags & 4)) {
+        store_row(dst0, tmem_o, st.x);
+        if (it.kind == kStageRightWithV) {
+          store_row(reinterpret_cast<T*>(g.y) + (((long long)it.eh * g.B + row) * g.M + it.tile) * kHead,
+                    tmem_o + kHead, st.y);
+        } else if (it.kind == kStageLeft) {
+          float o[32];
+          tmem_ld32(tmem_o + kHead, o);
+          g.cr[((long long)it.eh * g.M + row) * g.B + it.tile] = o[0];
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bar(kBarOEmpty + ob));
+      if (args.wait_deps) {
+        // hand the item to the publisher warp (4-deep ring)
+        if (!mbar_wait_abortable(bar(kBarPubFree + (n & 3)), ((uint32_t)(n >> 2) & 1u) ^ 1u, abort_flag)) {
+          give_up(502);
+          break;
+        }
+        mbar_arrive(bar(kBarDone + (n & 3)));
+      }
+    }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 192;");
     // =========================== softmax groups ==========================================
     const int grp = warp >> 2;                      // items with local index n = grp (mod 2)
     const int row = (warp & 3) * 32 + lane;         // tensor-memory lane = tile row
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     int n = 0;
-    long long trs[14][3];
+    bool alive = true;
+#if defined(MA_DIAG) && defined(MA_TRACE)
+    long long tr[8][8];
+    const bool tracer = (dbg_flags & 64) && (blockIdx.x == 0 || blockIdx.x == 77) && (tid & 127) == 0;
+    const long long t_loop = clock64();
+#define MA_TR(i) if (tracer && (n >> 1) < 8) tr[n >> 1][i] = clock64() - t_loop;
+#else
+#define MA_TR(i)
+#endif
     ItemCursor cur;
     for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid(); cur.next(), ++n) {
       if ((n & 1) != grp) continue;
       const Item it = cur.get();
+      MA_TR(0)
       const int slot = n % kSlots, sb = n & 1;
       const uint32_t ph2 = (uint32_t)(n >> 1) & 1u;
       const bool right = it.kind == kStageRight || it.kind == kStageRightWithV;
@@ -377,24 +465,36 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       const uint32_t sP = base + kOffP + sb * 2 * kTileBytes;
       const float* vec = reinterpret_cast<const float*>(base_ptr + kOffVec + slot * 512);
 
-      if (!mbar_wait_abortable(bar(kBarInFull + slot), (uint32_t)(n / kSlots) & 1u, abort_flag)) { give_up(401); break; }
-      if (!mbar_wait_abortable(bar(kBarSFull + sb), ph2, abort_flag)) { give_up(402); break; }
+      if (!mbar_wait_abortable(bar(kBarInFull + slot), (uint32_t)(n / kSlots) & 1u, abort_flag)) { give_up(401); alive = false; break; }
+      if (!mbar_wait_abortable(bar(kBarSFull + sb), ph2, abort_flag)) { give_up(402); alive = false; break; }
       tc_fence_after();
-      const bool trace = (args.dbg & 64) && blockIdx.x == 0 && (tid & 127) == 0 && n < 14;
-      const long long ts0 = trace ? clock64() - t_begin : 0;
+      MA_TR(1)
       const uint32_t tmem_s = tmem + lane_base + sb * 128;
 
+      // Two passes over the row of S, each a short loop over 64-column halves whose body handles two
+      // 32-column chunks in two register buffers: the tensor-memory load of the next chunk is in flight
+      // while the current one is processed, and the loop body stays small enough to sit in the
+      // instruction cache (a fully unrolled 128-column pass starves the schedulers of instructions).
       float row_scale = 0.f;
       if (right) row_scale = g.sm_scale / ((it.first ? 1.0f : vec[row]) + kEps);
-
-      // Tensor-memory loads are issued one 32-column chunk ahead of the arithmetic (two register
-      // buffers), and every reduction runs on four independent accumulators, so that a warp has
-      // enough independent work in flight to keep issuing.
       float ca[32], cb[32];
-      // ---- pass 1: row maximum -----------------------------------------------------------
       float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
-      auto max_chunk = [&](const float (&s)[32], int c) {
-        if (right) {
+      float s0 = 0.f, s1 = 0.f, t0 = 0.f, t1 = 0.f;
+      float mul, off;
+      // P row `row`, columns [col0, col0+32): K-major operand (row = M index) for the right-factor and
+      // output stages, MN-major operand holding P^T (row = K index) for the left-factor stage - the
+      // bytes land in the same place either way.
+      auto store_p = [&](const uint32_t (&packed)[16], int col0) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const uint32_t col = col0 + q4 * 8;
+          st_shared_v4(sP + (col >> 6) * kTileBytes + swz(row, (col & 63) >> 3), packed[q4 * 4], packed[q4 * 4 + 1],
+                       packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+        }
+      };
+      tmem_ld32_nowait(tmem_s, ca);
+      if (right) {
+        auto max_chunk = [&](const float (&s)[32]) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             m0 = max3(m0, s[i], s[i + 1]);
@@ -402,50 +502,22 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
             m2 = max3(m2, s[i + 4], s[i + 5]);
             m3 = max3(m3, s[i + 6], s[i + 7]);
           }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            const float4 x = *reinterpret_cast<const float4*>(vec + c * 32 + i);
-            const float4 y = *reinterpret_cast<const float4*>(vec + c * 32 + i + 4);
-            m0 = max3(m0, s[i] - x.x, s[i + 1] - x.y);
-            m1 = max3(m1, s[i + 2] - x.z, s[i + 3] - x.w);
-            m2 = max3(m2, s[i + 4] - y.x, s[i + 5] - y.y);
-            m3 = max3(m3, s[i + 6] - y.z, s[i + 7] - y.w);
-          }
+        };
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+          tmem_wait_ld(ca); tmem_ld32_nowait(tmem_s + 64 * h + 32, cb); max_chunk(ca);
+          tmem_wait_ld(cb); tmem_ld32_nowait(tmem_s + ((64 * h + 64) & 127), ca); max_chunk(cb);
         }
-      };
-      if (args.dbg & 1) {
-        m0 = 8.0f;
-        tmem_ld32_nowait(tmem_s, ca);
-      } else {
-      tmem_ld32_nowait(tmem_s, ca);
-      tmem_wait_ld(ca); tmem_ld32_nowait(tmem_s + 32, cb); max_chunk(ca, 0);
-      tmem_wait_ld(cb); tmem_ld32_nowait(tmem_s + 64, ca); max_chunk(cb, 1);
-      tmem_wait_ld(ca); tmem_ld32_nowait(tmem_s + 96, cb); max_chunk(ca, 2);
-      tmem_wait_ld(cb); tmem_ld32_nowait(tmem_s, ca);      max_chunk(cb, 3);   // chunk 0 again, for pass 2
-      }
-      const float vmax = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-      float mul, off;
-      if (right) {
+        MA_TR(2)
+        const float vmax = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
         const float top = fmaxf(vmax * row_scale, kEps);  // lower clamp on the row maximum
         mul = row_scale * kLog2e;
         off = top * kLog2e;
-      } else {
-        mul = kLog2e;
-        off = vmax * kLog2e;
-      }
-      if (trace) trs[n][1] = clock64() - t_begin;
-      if (!mbar_wait_abortable(bar(kBarPEmpty + sb), ph2 ^ 1u, abort_flag)) {
-        tmem_wait_ld(ca);
-        give_up(403);
-        break;
-      }
-
-      // ---- pass 2: exponentials, sums, P -------------------------------------------------
-      float s0 = 0.f, s1 = 0.f, t0 = 0.f, t1 = 0.f;
-      auto exp_chunk = [&](const float (&s)[32], int c) {
-        uint32_t packed[16];
-        if (right) {
+        MA_TR(3)
+        if (!mbar_wait_abortable(bar(kBarPEmpty + sb), ph2 ^ 1u, abort_flag)) { tmem_wait_ld(ca); give_up(403); alive = false; break; }
+        MA_TR(4)
+        auto exp_chunk = [&](const float (&s)[32], int col0) {
+          uint32_t packed[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             const float u0 = fmaf(s[i], mul, -off), u1 = fmaf(s[i + 1], mul, -off);
@@ -458,10 +530,45 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
             packed[i >> 1] = pack2<T>(e0, e1);
             packed[(i >> 1) + 1] = pack2<T>(e2, e3);
           }
-        } else {
+          store_p(packed, col0);
+        };
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+          tmem_wait_ld(ca); tmem_ld32_nowait(tmem_s + 64 * h + 32, cb); exp_chunk(ca, 64 * h);
+          tmem_wait_ld(cb);
+          if (h == 0) tmem_ld32_nowait(tmem_s + 64, ca);
+          else { tc_fence_before(); mbar_arrive(bar(kBarSEmpty + sb)); }  // S has been read in full
+          exp_chunk(cb, 64 * h + 32);
+        }
+      } else {
+        auto max_chunk = [&](const float (&s)[32], const float* c) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            const float4 x = *reinterpret_cast<const float4*>(c + i);
+            const float4 y = *reinterpret_cast<const float4*>(c + i + 4);
+            m0 = max3(m0, s[i] - x.x, s[i + 1] - x.y);
+            m1 = max3(m1, s[i + 2] - x.z, s[i + 3] - x.w);
+            m2 = max3(m2, s[i + 4] - y.x, s[i + 5] - y.y);
+            m3 = max3(m3, s[i + 6] - y.z, s[i + 7] - y.w);
+          }
+        };
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+          tmem_wait_ld(ca); tmem_ld32_nowait(tmem_s + 64 * h + 32, cb); max_chunk(ca, vec + 64 * h);
+          tmem_wait_ld(cb); tmem_ld32_nowait(tmem_s + ((64 * h + 64) & 127), ca); max_chunk(cb, vec + 64 * h + 32);
+        }
+        MA_TR(2)
+        const float vmax = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+        mul = kLog2e;
+        off = vmax * kLog2e;
+        MA_TR(3)
+        if (!mbar_wait_abortable(bar(kBarPEmpty + sb), ph2 ^ 1u, abort_flag)) { tmem_wait_ld(ca); give_up(403); alive = false; break; }
+        MA_TR(4)
+        auto exp_chunk = [&](const float (&s)[32], const float* c, int col0) {
+          uint32_t packed[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
-            const float4 x = *reinterpret_cast<const float4*>(vec + c * 32 + i);
+            const float4 x = *reinterpret_cast<const float4*>(c + i);
             const float e0 = ex2(fmaf(s[i] - x.x, mul, -off)), e1 = ex2(fmaf(s[i + 1] - x.y, mul, -off));
             const float e2 = ex2(fmaf(s[i + 2] - x.z, mul, -off)), e3 = ex2(fmaf(s[i + 3] - x.w, mul, -off));
             s0 += e0 + e1;
@@ -469,32 +576,19 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
             packed[i >> 1] = pack2<T>(e0, e1);
             packed[(i >> 1) + 1] = pack2<T>(e2, e3);
           }
+          store_p(packed, col0);
+        };
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+          tmem_wait_ld(ca); tmem_ld32_nowait(tmem_s + 64 * h + 32, cb); exp_chunk(ca, vec + 64 * h, 64 * h);
+          tmem_wait_ld(cb);
+          if (h == 0) tmem_ld32_nowait(tmem_s + 64, ca);
+          else { tc_fence_before(); mbar_arrive(bar(kBarSEmpty + sb)); }  // S has been read in full
+          exp_chunk(cb, vec + 64 * h + 32, 64 * h + 32);
         }
-        // Row `row`, columns [32c, 32c+32): K-major operand (row = M index) for the right-factor and
-        // output stages, MN-major operand holding P^T (row = K index) for the left-factor stage - the
-        // bytes land in the same place either way.
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const uint32_t col = c * 32 + q4 * 8;
-          st_shared_v4(sP + (col >> 6) * kTileBytes + swz(row, (col & 63) >> 3), packed[q4 * 4], packed[q4 * 4 + 1],
-                       packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
-        }
-      };
-      if (args.dbg & 2) {
-        tmem_wait_ld(ca);
-        s0 = 1.f;
-      } else {
-      tmem_wait_ld(ca); tmem_ld32_nowait(tmem_s + 32, cb); exp_chunk(ca, 0);
-      tmem_wait_ld(cb); tmem_ld32_nowait(tmem_s + 64, ca); exp_chunk(cb, 1);
-      tmem_wait_ld(ca); tmem_ld32_nowait(tmem_s + 96, cb); exp_chunk(ca, 2);
-      tmem_wait_ld(cb);
       }
-      // S has been read in full: hand the accumulator back before the last chunk's arithmetic
-      tc_fence_before();
-      mbar_arrive(bar(kBarSEmpty + sb));
-      if (!(args.dbg & 2)) exp_chunk(cb, 3);
       const float row_sum = s0 + s1, row_ent = t0 + t1;
-
+      MA_TR(5)
 
       float4 st = make_float4(0.f, 0.f, 0.f, 0.f);  // scale of O[:, :64], scale of O[:, 64:], cl, unused
       if (right) {
@@ -517,114 +611,32 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       } else {
         st.x = 1.0f / row_sum;
       }
-      // Row statistics for the epilogue.  The 4-deep ring cannot be overrun: item n+4 of this group
-      // needs P[(n+4)%2] free, i.e. the second contraction of item n+2, which needs O[n%2] free, i.e.
-      // the epilogue of item n finished.
+      // Row statistics for the epilogue group.  The 4-deep ring cannot be overrun: item n+4 of this
+      // group needs P[n%2] free twice over, i.e. the second contraction of item n+2, which needs
+      // O[n%2] free, i.e. the epilogue of item n finished.
       *reinterpret_cast<float4*>(base_ptr + kOffStats + ((n & 3) * 128 + row) * 16) = st;
       mbar_arrive(bar(kBarStat + (n & 3)));
+      MA_TR(6)
       fence_async_smem();
       mbar_arrive(bar(kBarPFull + sb));
-      if (trace) { trs[n][0] = ts0; trs[n][2] = clock64() - t_begin; }
+      MA_TR(7)
     }
-    if ((args.dbg & 64) && blockIdx.x == 0 && (tid & 127) == 0)
-      for (int i = grp; i < 14 && i < n; i += 2)
-        printf("softmax item %d: S ready %lld  max done %lld  P done %lld\n", i, trs[i][0], trs[i][1], trs[i][2]);
-  } else if (warp < kProducerWarp) {
-    // =========================== epilogue group =============================================
-    const int row = (warp & 3) * 32 + lane;
-    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    int n = 0;
-    long long tre[14][2];
-    ItemCursor cur;
-    for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid(); cur.next(), ++n) {
-      const Item it = cur.get();
-      const int ob = n & 1;
-      if (!mbar_wait_abortable(bar(kBarStat + (n & 3)), (uint32_t)(n >> 2) & 1u, abort_flag) ||
-          !mbar_wait_abortable(bar(kBarOFull + ob), (uint32_t)(n >> 1) & 1u, abort_flag)) {
-        give_up(501);
-        break;
-      }
-      tc_fence_after();
-      const bool trace = (args.dbg & 64) && blockIdx.x == 0 && row == 0 && n < 14;
-      const long long te0 = trace ? clock64() - t_begin : 0;
-      const float4 st = *reinterpret_cast<const float4*>(base_ptr + kOffStats + ((n & 3) * 128 + row) * 16);
-      const uint32_t tmem_o = tmem + lane_base + 256 + ob * 128;
-      T* dst0;
-      if (it.kind == kStageRight || it.kind == kStageRightWithV) {
-        dst0 = reinterpret_cast<T*>(g.al) + (((long long)it.eh * g.B + row) * g.M + it.tile) * kHead;
-        g.cl[((long long)it.eh * g.B + row) * g.M + it.tile] = st.z;
-      } else if (it.kind == kStageLeft) {
-        dst0 = reinterpret_cast<T*>(g.ar) + (((long long)it.eh * g.M + row) * g.B + it.tile) * kHead;
-      } else {
-        const int e = it.eh / g.H, h = it.eh - e * g.H;
-        dst0 = reinterpret_cast<T*>(const_cast<void*>(g.out.ptr)) + (long long)e * g.out.se + (long long)h * g.out.sh +
-               ((long long)row * g.B + it.tile) * g.out.sn;
-      }
-      // 64 accumulator columns -> one 128-byte row: both chunk loads in flight, then 8 x 16-byte stores
-      auto store_row = [&](T* dst, uint32_t taddr, float scale) {
-        float o0[32], o1[32];
-        tmem_ld32_nowait(taddr, o0);
-        tmem_ld32_nowait(taddr + 32, o1);
-        tmem_wait_ld(o0);
-        tmem_wait_ld(o1);
-#pragma unroll
-        for (int h8 = 0; h8 < 4; ++h8) {  // 32-byte stores: every touched sector is written whole
-          const float* p = (h8 < 2 ? o0 : o1) + (h8 & 1) * 16;
-          uint32_t w[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) w[i] = pack2<T>(p[2 * i] * scale, p[2 * i + 1] * scale);
-          st_global_v8(dst + h8 * 16, w);
-        }
-      };
-      if (!(args.dbg & 4)) store_row(dst0, tmem_o, st.x);
-      if (args.dbg & 4) {
-      } else if (it.kind == kStageRightWithV) {
-        store_row(reinterpret_cast<T*>(g.y) + (((long long)it.eh * g.B + row) * g.M + it.tile) * kHead, tmem_o + kHead,
-                  st.y);
-      } else if (it.kind == kStageLeft) {
-        float o[32];
-        tmem_ld32(tmem_o + kHead, o);
-        g.cr[((long long)it.eh * g.M + row) * g.B + it.tile] = o[0];
-      }
-      tc_fence_before();
-      mbar_arrive(bar(kBarOEmpty + ob));
-      if (trace) { tre[n][0] = te0; tre[n][1] = clock64() - t_begin; }
-      if (args.wait_deps) {
-        // hand the item to a publisher warp (4-deep ring), which makes the stores visible device-wide
-        // and counts the item as complete without holding this group up
-        if (!mbar_wait_abortable(bar(kBarPubFree + (n & 3)), ((uint32_t)(n >> 2) & 1u) ^ 1u, abort_flag)) {
-          give_up(502);
-          break;
-        }
-        mbar_arrive(bar(kBarDone + (n & 3)));
-      }
-    }
-    if ((args.dbg & 64) && blockIdx.x == 0 && row == 0)
-      for (int i = 0; i < 14 && i < n; ++i) printf("epilogue item %d: O ready %lld  stored %lld\n", i, tre[i][0], tre[i][1]);
-  } else if (warp >= kPublishWarp0) {
-    // =========================== publishers ===================================================
-    if (lane == 0 && args.wait_deps) {
-      const int par = warp - kPublishWarp0;
-      int n = 0;
-      ItemCursor cur;
-      for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid(); cur.next(), ++n) {
-        if ((n & 1) != par) continue;
-        const Item it = cur.get();
-        if (!mbar_wait_abortable(bar(kBarDone + (n & 3)), (uint32_t)(n >> 2) & 1u, abort_flag)) { give_up(601); break; }
-        if (it.stage != nst_all - 1) {  // nothing consumes the output stage
-          __threadfence();
-          atomicAdd(args.counters + it.eh * nst_all + it.stage, 1);
-        }
-        mbar_arrive(bar(kBarPubFree + (n & 3)));
-      }
-    }
+    (void)alive;
+#if defined(MA_DIAG) && defined(MA_TRACE)
+    if (tracer)
+      for (int i = 0; i < 8 && (2 * i + grp) < n; ++i)
+        printf("cta %d grp %d item %d: start %lld | S ready +%lld | ld+max +%lld | - +%lld | P free +%lld | exp +%lld | stats +%lld | arrive +%lld\n",
+               (int)blockIdx.x, grp, 2 * i + grp, tr[i][0], tr[i][1] - tr[i][0], tr[i][2] - tr[i][1], tr[i][3] - tr[i][2],
+               tr[i][4] - tr[i][3], tr[i][5] - tr[i][4], tr[i][6] - tr[i][5], tr[i][7] - tr[i][6]);
+#endif
+
+
   }
 
   // ---- teardown ------------------------------------------------------------------------------
   tc_fence_before();
   __syncthreads();
-  if ((args.dbg & 64) && blockIdx.x == 0 && tid == 0) printf("cta 0 all roles done at %lld\n", clock64() - t_begin);
-  if (warp == kMmaWarp) {
+  if (warp == kMma1Warp) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
   }
 }
@@ -647,10 +659,10 @@ cudaError_t launch_fused(const TcPlan* plan, const Geometry& g, int* counters, i
   a.group = g.E * g.H < 4 ? g.E * g.H : 4;
   a.wait_deps = wait_deps;
   a.counters = counters;
-  {
-    const char* d = getenv("MA_B200_DEBUG");
-    a.dbg = d ? atoi(d) : 0;
-  }
+  a.dbg = 0;
+#ifdef MA_DIAG
+  if (const char* d = getenv("MA_B200_DEBUG")) a.dbg = atoi(d);
+#endif
   const int total = (stage_end - stage_begin) * kTile * g.E * g.H;
   const int grid = total < sms ? total : sms;
   const void* fn = plan->qk_dtype == MA_B200_BF16 ? (const void*)fused_kernel<__nv_bfloat16>

@@ -86,6 +86,23 @@ __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same instruction with each descriptor given as its low word; the high word (stride between
+// 8-row groups, descriptor version, swizzle mode) is common to every operand of these kernels.
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t addr, uint32_t lbo_bytes) {
+  return ((addr & 0x3FFFF) >> 4) | (((lbo_bytes >> 4) & 0x3FFF) << 16);
+}
+constexpr uint32_t kSmemDescHi = ((1024u >> 4) & 0x3FFF) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ void mma_f16_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "mov.b64 da, {%1, %5};\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kSmemDescHi)
+      : "memory");
+}
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -176,6 +193,25 @@ __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
 // Byte offset of 16-byte chunk `chunk` (0..7) of row `row` in a [rows x 128 B] tile with 128-byte swizzle.
 __device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t chunk) { return row * 128u + ((chunk ^ (row & 7u)) << 4); }
 
+// Bounded, abortable wait for roles that are not latency-critical: backs off between attempts so that
+// the waiting warp leaves the issue slots of its scheduler to the warps doing arithmetic.
+__device__ __forceinline__ bool mbar_wait_polite(uint32_t bar, uint32_t parity, const volatile int* abort_flag,
+                                                 unsigned sleep_ns) {
+  for (int it = 0; it < (1 << 21); ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+    __nanosleep(sleep_ns);
+    if ((it & 255) == 255 && *abort_flag != 0) return false;
+  }
+  return false;
+}
 // Non-blocking test of the phase with the given parity.
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t done;
