@@ -15,10 +15,10 @@
 // item schedule needs for forward progress.
 //
 // Inside a CTA (512 threads, one CTA per SM, all 512 tensor-memory columns):
-//   warps 0-3, 4-7   two softmax groups on alternating items, one tile row per thread: the whole row
-//              of S is read into registers in one tcgen05.ld round trip (raised register budget via
-//              setmaxnreg), two passes over the registers (max; exp, sums, entropy), P (16-bit) to
-//              swizzled shared memory, row statistics to a small ring for the epilogue
+//   warps 0-3, 4-7   two softmax groups on alternating items, one tile row per thread: two passes
+//              over the row of S (max; exp, sums, entropy) in short loops that read 32-column
+//              chunks with tcgen05.ld one chunk ahead of the arithmetic, P (16-bit) to swizzled
+//              shared memory, row statistics to a small ring for the epilogue
 //   warps 8-11 epilogue group: waits for O[n%2], scales it by the row statistics and stores rows to
 //              global memory with 32-byte stores (it absorbs the latency of the second contraction so
 //              that the softmax groups never wait for it)
@@ -625,8 +625,8 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
 #if defined(MA_DIAG) && defined(MA_TRACE)
     if (tracer)
       for (int i = 0; i < 8 && (2 * i + grp) < n; ++i)
-        printf("cta %d grp %d item %d: start %lld | S ready +%lld | ld+max +%lld | - +%lld | P free +%lld | exp +%lld | stats +%lld | arrive +%lld\n",
-               (int)blockIdx.x, grp, 2 * i + grp, tr[i][0], tr[i][1] - tr[i][0], tr[i][2] - tr[i][1], tr[i][3] - tr[i][2],
+        printf("kind %d cta %d grp %d item %d: start %lld | S ready +%lld | ld+max +%lld | - +%lld | P free +%lld | exp +%lld | stats +%lld | arrive +%lld\n",
+               dbg_flags >> 8, (int)blockIdx.x, grp, 2 * i + grp, tr[i][0], tr[i][1] - tr[i][0], tr[i][2] - tr[i][1], tr[i][3] - tr[i][2],
                tr[i][4] - tr[i][3], tr[i][5] - tr[i][4], tr[i][6] - tr[i][5], tr[i][7] - tr[i][6]);
 #endif
 
