@@ -56,32 +56,36 @@ constexpr int kMma2Warp = 14;
 constexpr int kPublishWarp = 15;
 constexpr int kThreads = 16 * 32;
 
-constexpr int kSlots = 3;
-constexpr uint32_t kSlotBytes = 3 * kTileBytes;  // A | B | V
+// Operand tiles live in a ring of nine 16 KB tiles.  An item takes two consecutive tiles (A, B) or
+// three (A, B, V) - never wrapping: if the tail of the ring is too short it is skipped - so up to four
+// items of the two-tile kinds are in flight, which is what hides the latency of their loads.
+constexpr int kNumBarsConst = 32;
+constexpr int kRingTiles = 9;
+constexpr int kItemsInFlight = 4;  // depth of the per-item barrier / row-vector rings
 constexpr uint32_t kOffSlots = 0;
-constexpr uint32_t kOffP = kOffSlots + kSlots * kSlotBytes;  // 2 x 32 KB
-constexpr uint32_t kOffSv = kOffP + 2 * 2 * kTileBytes;      // 2 x 4 KB (per P buffer; left stage)
-constexpr uint32_t kOffVec = kOffSv + 2 * 4096;              // 3 x 512 B (per slot)
+constexpr uint32_t kOffP = kOffSlots + kRingTiles * kTileBytes;  // 2 x 32 KB
+constexpr uint32_t kOffSv = kOffP + 2 * 2 * kTileBytes;          // 2 x 4 KB (per P buffer; left stage)
+constexpr uint32_t kOffVec = kOffSv + 2 * 4096;                  // 4 x 512 B (per item in flight)
 static_assert(kOffP % 1024 == 0 && kOffSv % 1024 == 0, "swizzled operands need 1024-byte alignment");
-constexpr uint32_t kOffStats = kOffVec + kSlots * 512;       // 4 x 128 x float4 row statistics
-constexpr uint32_t kOffBar = kOffStats + 4 * 128 * 16;
-constexpr uint32_t kSmemUsed = kOffBar + 256;
+constexpr uint32_t kOffStats = kOffVec + kItemsInFlight * 512;   // 4 x 128 x 3 floats of row statistics
+constexpr uint32_t kOffBar = kOffStats + 4 * 128 * 12;
+constexpr uint32_t kSmemUsed = kOffBar + 8 * kNumBarsConst + 16;
 constexpr uint32_t kSmemBytes = kSmemUsed + 1024;
 
 // mbarrier indices (8 bytes each)
 enum {
-  kBarInFull = 0,    // [3] operand slot filled by TMA
-  kBarInEmpty = 3,   // [3] operand slot released by the second contraction
-  kBarSFull = 6,     // [2] S accumulator ready
-  kBarSEmpty = 8,    // [2] S accumulator read by the softmax group
-  kBarPFull = 10,    // [2] P written
-  kBarPEmpty = 12,   // [2] P consumed by the second contraction
-  kBarOFull = 14,    // [2] O accumulator ready
-  kBarOEmpty = 16,   // [2] O accumulator read by the epilogue group
-  kBarDone = 18,     // [4] item stored to global memory by all 128 epilogue threads
-  kBarPubFree = 22,  // [4] completion of that item published
-  kBarStat = 26,     // [4] row statistics of the item written by its softmax group
-  kNumBars = 30
+  kBarInFull = 0,    // [4] operand tiles of an item filled by TMA
+  kBarInEmpty = 4,   // [4] operand tiles of an item released by the second contraction
+  kBarSFull = 8,     // [2] S accumulator ready
+  kBarSEmpty = 10,   // [2] S accumulator read by the softmax group
+  kBarPFull = 12,    // [2] P written
+  kBarPEmpty = 14,   // [2] P consumed by the second contraction
+  kBarOFull = 16,    // [2] O accumulator ready
+  kBarOEmpty = 18,   // [2] O accumulator read by the epilogue group
+  kBarDone = 20,     // [4] item stored to global memory by all 128 epilogue threads
+  kBarPubFree = 24,  // [4] completion of that item published
+  kBarStat = 28,     // [4] row statistics of the item written by its softmax group
+  kNumBars = 32
 };
 
 struct FusedArgs {
@@ -101,6 +105,7 @@ struct Item {
 struct ItemCursor {
   int gi, sl, hh, tile, gh;  // group, stage within the launch, head within the group, tile, heads in this group
   int idx, total, stride, nst, group, EH, stage_begin, last_stage;
+  int ring_pos;  // next free tile of the operand ring (advanced by take())
 
   __device__ __forceinline__ void init(int first_idx, int stride_, const Geometry& g, const FusedArgs& a) {
     EH = g.E * g.H;
@@ -115,6 +120,7 @@ struct ItemCursor {
 #endif
     stride = stride_;
     idx = first_idx;
+    ring_pos = 0;
     const int per_group = nst * group * kTile;
     gi = idx / per_group;
     int r = idx - gi * per_group;
@@ -153,6 +159,23 @@ struct ItemCursor {
     it.first = it.stage == 0;
     return it;
   }
+  // The current item plus its place in the operand ring; call exactly once per item, in item order.
+  // first_tile: index of the item's A tile (B and V follow it); skipped: tiles wasted at the ring's tail.
+  __device__ __forceinline__ Item take(int* first_tile, int* tiles, int* skipped) {
+    const Item it = get();
+    const int k = (it.kind == kStageRightWithV || it.kind == kStageOutput) ? 3 : 2;
+    int sk = 0;
+    if (ring_pos + k > kRingTiles) {
+      sk = kRingTiles - ring_pos;
+      ring_pos = 0;
+    }
+    *first_tile = ring_pos;
+    *tiles = k;
+    *skipped = sk;
+    ring_pos += k;
+    if (ring_pos == kRingTiles) ring_pos = 0;
+    return it;
+  }
 };
 
 template <typename T>
@@ -178,7 +201,8 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
 
 
   if (tid == 0) {
-    for (int i = 0; i < 3; ++i) { mbar_init(bar(kBarInFull + i), 1); mbar_init(bar(kBarInEmpty + i), 1); }
+    static_assert(kNumBars == kNumBarsConst, "barrier count");
+    for (int i = 0; i < kItemsInFlight; ++i) { mbar_init(bar(kBarInFull + i), 1); mbar_init(bar(kBarInEmpty + i), 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(kBarSFull + i), 1);
       mbar_init(bar(kBarSEmpty + i), 128);
@@ -226,12 +250,15 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
     // =========================== TMA producer ===========================================
     if (lane == 0) {
       int n = 0, issued = 0;
+      int free_tiles = kRingTiles, oldest = 0;     // ring accounting: items [oldest, n) hold tiles
+      int held[kItemsInFlight] = {0, 0, 0, 0};     // tiles (incl. skipped tail) held by item m, at m % 4
       ItemCursor cur;
-      for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid(); cur.next(), ++n) {
-        const Item it = cur.get();
+      bool ok = true;
+      for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid() && ok; cur.next(), ++n) {
+        int t0, ntiles, skipped;
+        const Item it = cur.take(&t0, &ntiles, &skipped);
         const int e = it.eh / g.H, h = it.eh - e * g.H;
-        const int slot = n % kSlots;
-        const uint32_t ph = (uint32_t)(n / kSlots) & 1u;
+        const int slot = n % kItemsInFlight;
         if (args.wait_deps && it.stage > 0) {
           const int* ctr = args.counters + it.eh * nst_all + (it.stage - 1);
           bool ready = false;
@@ -243,18 +270,26 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           if (!ready) { give_up(201); break; }
           fence_proxy_async_all();  // the state was written with ordinary stores; the loads below are TMA
         }
-        if (!mbar_wait_abortable(bar(kBarInEmpty + slot), ph ^ 1u, abort_flag)) { give_up(202); break; }
-        const uint32_t sA = base + kOffSlots + slot * kSlotBytes, sB = sA + kTileBytes, sV = sB + kTileBytes;
+        // make room: items release their tiles in order (second contraction of item m done)
+        while (free_tiles < ntiles + skipped || n - oldest >= kItemsInFlight) {
+          if (!mbar_wait_abortable(bar(kBarInEmpty + oldest % kItemsInFlight), (uint32_t)(oldest / kItemsInFlight) & 1u,
+                                   abort_flag)) {
+            give_up(202);
+            ok = false;
+            break;
+          }
+          free_tiles += held[oldest % kItemsInFlight];
+          ++oldest;
+        }
+        if (!ok) break;
+        held[slot] = ntiles + skipped;
+        free_tiles -= ntiles + skipped;
+        const uint32_t sA = base + kOffSlots + t0 * kTileBytes, sB = sA + kTileBytes, sV = sB + kTileBytes;
         const uint32_t vec = base + kOffVec + slot * 512;
         const uint32_t full = bar(kBarInFull + slot);
         const bool right = it.kind == kStageRight || it.kind == kStageRightWithV;
-        const bool three = it.kind == kStageRightWithV || it.kind == kStageOutput;
+        const bool three = ntiles == 3;
         const bool has_vec = !(right && it.first);
-        if ((dbg_flags & 16) && n >= kSlots) {
-          mbar_arrive(full);
-          issued = n + 1;
-          continue;
-        }
         mbar_expect_tx(full, (three ? 3u : 2u) * kTileBytes + (has_vec ? 512u : 0u));
         if (right) {
           if (it.first) tma_load_5d(sA, &maps.q_blk, full, 0, 0, it.tile, h, e);
@@ -271,8 +306,8 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         issued = n + 1;
       }
       // Drain: make sure every copy this thread started has landed before the CTA may exit.
-      for (int m = max(0, issued - kSlots); m < issued; ++m)
-        (void)mbar_wait(bar(kBarInFull + m % kSlots), (uint32_t)(m / kSlots) & 1u);
+      for (int m = max(0, issued - kItemsInFlight); m < issued; ++m)
+        (void)mbar_wait(bar(kBarInFull + m % kItemsInFlight), (uint32_t)(m / kItemsInFlight) & 1u);
     }
   } else if (warp == kMma1Warp) {
     // =========================== MMA issuer 1: S = A B^T ====================================
@@ -281,17 +316,20 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
     // n+1 may depend on the completion of item n of this same CTA, so the second contraction of item n
     // must never queue behind a wait for item n+1.
     if (lane == 0) {
-      const uint32_t dA0 = smem_desc_lo(base + kOffSlots, 16);  // slot tile A, K-major; tile B follows it
-      constexpr uint32_t kSlotStep = kSlotBytes >> 4, kTileStep = kTileBytes >> 4;
+      const uint32_t dA0 = smem_desc_lo(base + kOffSlots, 16);  // ring tile 0 as a K-major operand; B follows A
+      constexpr uint32_t kTileStep = kTileBytes >> 4;
       constexpr uint32_t idesc1 = instr_desc(kFmt, 0, 0, kTile, kTile);
       int n = 0;
-      for (int idx = blockIdx.x; idx < total; idx += gridDim.x, ++n) {
-        const int slot = n % kSlots, sb = n & 1;
-        if (!mbar_wait_abortable(bar(kBarInFull + slot), (uint32_t)(n / kSlots) & 1u, abort_flag)) { give_up(301); break; }
+      ItemCursor cur;
+      for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid(); cur.next(), ++n) {
+        int t0, ntiles, skipped;
+        (void)cur.take(&t0, &ntiles, &skipped);
+        const int slot = n % kItemsInFlight, sb = n & 1;
+        if (!mbar_wait_abortable(bar(kBarInFull + slot), (uint32_t)(n / kItemsInFlight) & 1u, abort_flag)) { give_up(301); break; }
         if (!mbar_wait_abortable(bar(kBarSEmpty + sb), ((uint32_t)(n >> 1) & 1u) ^ 1u, abort_flag)) { give_up(302); break; }
         tc_fence_after();
         if (!(dbg_flags & 8)) {
-          const uint32_t dA = dA0 + slot * kSlotStep, dB = dA + kTileStep;
+          const uint32_t dA = dA0 + t0 * kTileStep, dB = dA + kTileStep;
 #pragma unroll
           for (int kk = 0; kk < kHead / 16; ++kk) mma_f16_lo(tmem + sb * 128, dA + kk * 2, dB + kk * 2, idesc1, kk > 0);
         }
@@ -304,20 +342,22 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       const uint32_t dP_k0 = smem_desc_lo(base + kOffP, 16);           // P as K-major A operand
       const uint32_t dP_mn0 = smem_desc_lo(base + kOffP, kTileBytes);   // P^T as MN-major A operand
       const uint32_t dS0 = smem_desc_lo(base + kOffSv, 16);             // 16 x 128 K-major operand (1/rowsum)
-      const uint32_t dBmn0 = smem_desc_lo(base + kOffSlots + kTileBytes, kTileBytes);  // slot tile B (| V), MN-major
-      constexpr uint32_t kSlotStep = kSlotBytes >> 4, kTileStep = kTileBytes >> 4, kPStep = (2 * kTileBytes) >> 4;
+      const uint32_t dTmn0 = smem_desc_lo(base + kOffSlots, kTileBytes);  // ring tile 0 as an MN-major operand
+      constexpr uint32_t kTileStep = kTileBytes >> 4, kPStep = (2 * kTileBytes) >> 4;
       int n = 0;
       ItemCursor cur;
       for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid(); cur.next(), ++n) {
-        const int kind = cur.get().kind;
-        const int pb = n & 1, slot = n % kSlots;
+        int t0, ntiles, skipped;
+        const int kind = cur.take(&t0, &ntiles, &skipped).kind;
+        const int pb = n & 1, slot = n % kItemsInFlight;
         const uint32_t ph2 = (uint32_t)(n >> 1) & 1u;
         if (!mbar_wait_abortable(bar(kBarPFull + pb), ph2, abort_flag)) { give_up(303); break; }
         if (!mbar_wait_abortable(bar(kBarOEmpty + pb), ph2 ^ 1u, abort_flag)) { give_up(304); break; }
         tc_fence_after();
         if (!(dbg_flags & 8)) {
           const uint32_t dPk = dP_k0 + pb * kPStep, dPmn = dP_mn0 + pb * kPStep;
-          const uint32_t dB = dBmn0 + slot * kSlotStep, dV = dB + kTileStep;
+          // tiles of the item: A (left stage: q' written over it), B, V
+          const uint32_t dA = dTmn0 + t0 * kTileStep, dB = dA + kTileStep, dV = dB + kTileStep;
           const uint32_t tmem_o = tmem + 256 + pb * 128;
           if (kind == kStageRight) {
             constexpr uint32_t idesc = instr_desc(kFmt, 0, 1, kHead, kTile);
@@ -325,7 +365,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
             for (int kk = 0; kk < kTile / 16; ++kk)
               mma_f16_lo(tmem_o, dPk + ((kk >> 2) * kTileStep + (kk & 3) * 2), dB + kk * 128, idesc, kk > 0);
           } else if (kind == kStageRightWithV) {
-            // the V tile follows the B tile in the slot: second 64-column atom of a 128-wide operand
+            // the V tile follows the B tile in the ring: second 64-column atom of a 128-wide operand
             constexpr uint32_t idesc = instr_desc(kFmt, 0, 1, 2 * kHead, kTile);
 #pragma unroll
             for (int kk = 0; kk < kTile / 16; ++kk)
@@ -336,7 +376,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
             const uint32_t dS = dS0 + pb * (4096 >> 4);
 #pragma unroll
             for (int kk = 0; kk < kTile / 16; ++kk) {
-              mma_f16_lo(tmem_o, dPmn + kk * 128, dV + kk * 128, idesc_q, kk > 0);
+              mma_f16_lo(tmem_o, dPmn + kk * 128, dA + kk * 128, idesc_q, kk > 0);
               mma_f16_lo(tmem_o + kHead, dPmn + kk * 128, dS + ((kk >> 2) * 128 + (kk & 3) * 2), idesc_s, kk > 0);
             }
           } else {
@@ -385,7 +425,8 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         break;
       }
       tc_fence_after();
-      const float4 st = *reinterpret_cast<const float4*>(base_ptr + kOffStats + ((n & 3) * 128 + row) * 16);
+      const float* stp = reinterpret_cast<const float*>(base_ptr + kOffStats) + ((n & 3) * 128 + row) * 3;
+      const float4 st = make_float4(stp[0], stp[1], stp[2], 0.f);
       const uint32_t tmem_o = tmem + lane_base + 256 + ob * 128;
       T* dst0;
       if (it.kind == kStageRight || it.kind == kStageRightWithV) {
@@ -455,17 +496,18 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
 #endif
     ItemCursor cur;
     for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid(); cur.next(), ++n) {
+      int tile0, ntiles, skipped;
+      const Item it = cur.take(&tile0, &ntiles, &skipped);  // every item moves the ring position
       if ((n & 1) != grp) continue;
-      const Item it = cur.get();
       MA_TR(0)
-      const int slot = n % kSlots, sb = n & 1;
+      const int slot = n % kItemsInFlight, sb = n & 1;
       const uint32_t ph2 = (uint32_t)(n >> 1) & 1u;
       const bool right = it.kind == kStageRight || it.kind == kStageRightWithV;
-      const uint32_t sA = base + kOffSlots + slot * kSlotBytes, sV = sA + 2 * kTileBytes;
+      const uint32_t sA = base + kOffSlots + tile0 * kTileBytes;
       const uint32_t sP = base + kOffP + sb * 2 * kTileBytes;
       const float* vec = reinterpret_cast<const float*>(base_ptr + kOffVec + slot * 512);
 
-      if (!mbar_wait_abortable(bar(kBarInFull + slot), (uint32_t)(n / kSlots) & 1u, abort_flag)) { give_up(401); alive = false; break; }
+      if (!mbar_wait_abortable(bar(kBarInFull + slot), (uint32_t)(n / kItemsInFlight) & 1u, abort_flag)) { give_up(401); alive = false; break; }
       if (!mbar_wait_abortable(bar(kBarSFull + sb), ph2, abort_flag)) { give_up(402); alive = false; break; }
       tc_fence_after();
       MA_TR(1)
@@ -600,10 +642,10 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         const float inv = 1.0f / row_sum;
         st.x = 1.0f;
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {  // q' = q / rowsum into the third tile of the slot
+        for (int ch = 0; ch < 8; ++ch) {  // q' = q / rowsum, in place (S = A B^T has consumed the tile)
           const uint4 v = ld_shared_v4(sA + swz(row, ch));
           const float2 a = unpack2<T>(v.x), b = unpack2<T>(v.y), c2 = unpack2<T>(v.z), d = unpack2<T>(v.w);
-          st_shared_v4(sV + swz(row, ch), pack2<T>(a.x * inv, a.y * inv), pack2<T>(b.x * inv, b.y * inv),
+          st_shared_v4(sA + swz(row, ch), pack2<T>(a.x * inv, a.y * inv), pack2<T>(b.x * inv, b.y * inv),
                        pack2<T>(c2.x * inv, c2.y * inv), pack2<T>(d.x * inv, d.y * inv));
         }
         T* srow = reinterpret_cast<T*>(base_ptr + kOffSv + sb * 4096 + (row >> 6) * 2048);
@@ -614,7 +656,12 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       // Row statistics for the epilogue group.  The 4-deep ring cannot be overrun: item n+4 of this
       // group needs P[n%2] free twice over, i.e. the second contraction of item n+2, which needs
       // O[n%2] free, i.e. the epilogue of item n finished.
-      *reinterpret_cast<float4*>(base_ptr + kOffStats + ((n & 3) * 128 + row) * 16) = st;
+      {
+        float* stp = reinterpret_cast<float*>(base_ptr + kOffStats) + ((n & 3) * 128 + row) * 3;
+        stp[0] = st.x;
+        stp[1] = st.y;
+        stp[2] = st.z;
+      }
       mbar_arrive(bar(kBarStat + (n & 3)));
       MA_TR(6)
       fence_async_smem();
