@@ -41,7 +41,7 @@ int validate(const ma_b200_problem* p, bool need_pointers) {
     return fail(MA_B200_INVALID_ARGUMENT, "unknown dtype");
   if (!(p->qk_dtype == p->v_dtype || p->v_dtype == MA_B200_F32))
     return fail(MA_B200_UNSUPPORTED, "v_dtype must equal qk_dtype or be f32");
-  if (p->kernel < MA_B200_KERNEL_AUTO || p->kernel > MA_B200_KERNEL_TCGEN05_TILE)
+  if (p->kernel < MA_B200_KERNEL_AUTO || p->kernel > MA_B200_KERNEL_WARP_MMA)
     return fail(MA_B200_INVALID_ARGUMENT, "unknown kernel family");
   if ((long long)p->E * p->H > 0x7fffffffLL / 2) return fail(MA_B200_INVALID_ARGUMENT, "E*H too large");
   if (need_pointers) {
@@ -86,9 +86,15 @@ ma::Geometry make_geometry(const ma_b200_problem* p) {
 int resolve_kernel(const ma_b200_problem* p, const ma::Geometry& g, int* kernel) {
   const char* why = "";
   const bool tc_ok = ma::tc_supported(g, p->qk_dtype, p->v_dtype, &why);
-  if (p->kernel >= MA_B200_KERNEL_TCGEN05 && !tc_ok)
+  const bool wants_tc = p->kernel >= MA_B200_KERNEL_TCGEN05 && p->kernel <= MA_B200_KERNEL_TCGEN05_TILE;
+  if (wants_tc && !tc_ok)
     return fail(MA_B200_UNSUPPORTED, std::string("tcgen05 path cannot run this problem: ") + why);
-  if (p->kernel == MA_B200_KERNEL_AUTO) *kernel = tc_ok ? MA_B200_KERNEL_TCGEN05 : MA_B200_KERNEL_GENERIC;
+  const char* why_w = "";
+  const bool warp_ok = ma::warp_supported(g, p->qk_dtype, p->v_dtype, &why_w);
+  if (p->kernel == MA_B200_KERNEL_WARP_MMA && !warp_ok)
+    return fail(MA_B200_UNSUPPORTED, std::string("warp-level tensor-core path cannot run this problem: ") + why_w);
+  if (p->kernel == MA_B200_KERNEL_AUTO)
+    *kernel = tc_ok ? MA_B200_KERNEL_TCGEN05 : (warp_ok ? MA_B200_KERNEL_WARP_MMA : MA_B200_KERNEL_GENERIC);
   else *kernel = p->kernel;
   if (*kernel == MA_B200_KERNEL_GENERIC) {
     const size_t need = ma::generic_stage_smem_bytes(g, g.B > g.M ? ma::kStageRight : ma::kStageLeft);
@@ -155,7 +161,7 @@ int run_forward(const ma_b200_problem* p, void* workspace, size_t workspace_byte
   int* counters = reinterpret_cast<int*>(ws + L.counters);
 
   ma::TcPlan* plan = nullptr;
-  if (L.kernel >= MA_B200_KERNEL_TCGEN05) {
+  if (L.kernel >= MA_B200_KERNEL_TCGEN05 && L.kernel <= MA_B200_KERNEL_TCGEN05_TILE) {
     const char* err = "";
     rc = ma::tc_plan_create(g, p->qk_dtype, &plan, &err);
     if (rc != MA_B200_OK) return fail(rc, std::string("tcgen05 plan: ") + err);
@@ -174,6 +180,7 @@ int run_forward(const ma_b200_problem* p, void* workspace, size_t workspace_byte
     if (L.kernel == MA_B200_KERNEL_TCGEN05_TILE) e = ma::launch_tc_stage(plan, g, kind, first, stream);
     else if (L.kernel == MA_B200_KERNEL_TCGEN05_STAGED)
       e = ma::launch_fused(plan, g, counters, stage_idx, stage_idx + 1, 0, stream);
+    else if (L.kernel == MA_B200_KERNEL_WARP_MMA) e = ma::launch_warp_stage(g, p->qk_dtype, kind, first, stream);
     else e = ma::launch_generic_stage(g, p->qk_dtype, p->v_dtype, kind, first, stream);
     ++stage_idx;
     if (ev != nullptr) cudaEventRecord(ev[stage_idx], stream);

@@ -71,6 +71,10 @@ cudaError_t launch_generic_stage(const Geometry& g, int qk_dtype, int v_dtype, S
                                  cudaStream_t stream);
 size_t generic_stage_smem_bytes(const Geometry& g, StageKind kind);
 
+// Warp-level tensor-core stage kernels (16-bit, block size and count <= 128, D <= 80).
+bool warp_supported(const Geometry& g, int qk_dtype, int v_dtype, const char** why);
+cudaError_t launch_warp_stage(const Geometry& g, int qk_dtype, StageKind kind, bool first, cudaStream_t stream);
+
 // Tensor-core (tcgen05) path.
 bool tc_supported(const Geometry& g, int qk_dtype, int v_dtype, const char** why);
 // Prepares per-call tensor maps; returns an opaque plan used by launch_tc_stage.

@@ -1,0 +1,115 @@
+// Warp-level tensor-core stage kernels for 16-bit inputs with block size and block count up to 128:
+// the ViT / RoBERTa / DiT shapes (b = 14..32, N <= 1024, D = 64 or 72) and the b = 64 op sweep.
+//
+// These shapes are HBM-bound (intensity ~1.25*b FLOP/B) and their blocks are far smaller than a
+// tcgen05 tile, so the job here is to move each operand once, with every row masked / zero-padded in
+// flight, and to keep the small contractions on tensor cores: mma.sync m16n8k16 with fp32
+// accumulation, fragments read from padded shared-memory tiles with ldmatrix.  One CTA works on one
+// tile - (head, key block m) for the right-factor stages, (head, column j) for the left-factor and
+// output stages - with one warp per 16 rows.  The row softmax runs on the accumulator fragments
+// (a row lives in one quad of lanes), and the normalised factor goes back into the second
+// contraction straight from registers (right-factor / output) or through a shared-memory tile that
+// is read transposed (left-factor, which contracts over the rows).
+//
+// Semantics follow the reference stage for stage (reference: ma/ma_torch.py:10-62): invalid keys at
+// -inf, row maximum clamped from below at eps, eps in the denominator, floor at FLT_MIN, fully
+// masked key blocks give ~0 factors and logit 0, invalid queries zeroed in the left-factor stage
+// only, padding rows dropped on output.
+#include <math.h>
+
+#include "ma_common.cuh"
+
+namespace ma {
+namespace {
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t addr, uint32_t (&r)[2]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2_trans(uint32_t addr, uint32_t (&r)[2]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]);
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+template <>
+__device__ __forceinline__ void mma16816<__half>(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack_pair(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <>
+__device__ __forceinline__ uint32_t pack_pair<__half>(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ float quad_max(float v) {
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+  return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+}
+__device__ __forceinline__ float quad_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  return v + __shfl_xor_sync(0xffffffffu, v, 2);
+}
+
+// Copies `rows` rows of `width` 16-bit elements (width a multiple of 8) into a shared tile with row
+// pitch `pitch` elements, zero-filling rows whose source pointer is null, columns [width, wpad) and
+// rows [rows, rpad).  row_ptr(r) returns the global row or nullptr.
+template <typename T, typename RowFn>
+__device__ __forceinline__ void load_tile(T* tile, int pitch, int rows, int rpad, int width, int wpad, RowFn row_ptr) {
+  const int chunks = wpad >> 3;
+  for (int i = threadIdx.x; i < rpad * chunks; i += blockDim.x) {
+    const int r = i / chunks, c = (i - r * chunks) << 3;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < rows && c < width) {
+      const T* src = row_ptr(r);
+      if (src != nullptr) v = *reinterpret_cast<const uint4*>(src + c);
+    }
+    *reinterpret_cast<uint4*>(tile + r * pitch + c) = v;
+  }
+}
+
+__device__ __forceinline__ bool pos_valid(const Geometry& g, int e, int p) {
+  const int n = p - g.pad_off;
+  if (n < 0 || n >= g.N) return false;
+  return g.mask == nullptr || g.mask[(long long)e * g.mask_se + n] != 0;
+}
+template <typename T>
+__device__ __forceinline__ const T* user_row(const View4& t, int e, int h, int p, const Geometry& g) {
+  const int n = p - g.pad_off;
+  if (n < 0 || n >= g.N) return nullptr;
+  return reinterpret_cast<const T*>(t.ptr) + (long long)e * t.se + (long long)h * t.sh + (long long)n * t.sn;
+}
+
+}  // namespace
+}  // namespace ma
+
+#include "ma_warp_kernels.inc"

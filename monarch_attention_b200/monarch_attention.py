@@ -152,6 +152,8 @@ register_impl("b200-generic", _generic)
 register_impl("b200-tcgen05", _tcgen05)
 register_impl("b200-tcgen05-staged",
               lambda q, k, v, m, T, B, pp: monarch_attention_b200(q, k, v, m, T, B, pp, kernel=_cabi.KERNEL_TCGEN05_STAGED))
+register_impl("b200-warp-mma",
+              lambda q, k, v, m, T, B, pp: monarch_attention_b200(q, k, v, m, T, B, pp, kernel=_cabi.KERNEL_WARP_MMA))
 register_impl("b200-tcgen05-tile",
               lambda q, k, v, m, T, B, pp: monarch_attention_b200(q, k, v, m, T, B, pp, kernel=_cabi.KERNEL_TCGEN05_TILE))
 
@@ -161,8 +163,8 @@ class MonarchAttention(nn.Module):
 
     ``impl`` selects the kernel family: "b200" (default: fused tensor-core kernel when the
     problem fits it, otherwise the generic path), "b200-generic", "b200-tcgen05" (fused, one
-    launch), "b200-tcgen05-staged" (same kernel, one launch per stage) or "b200-tcgen05-tile"
-    (one tile per CTA).  The reference's
+    launch), "b200-tcgen05-staged" (same kernel, one launch per stage), "b200-tcgen05-tile"
+    (one tile per CTA) or "b200-warp-mma" (warp-level tensor-core kernels for small blocks).  The reference's
     "torch" and "triton" implementations are not part of this library; asking for an
     unknown name raises ``ValueError`` exactly as the reference does.
     """

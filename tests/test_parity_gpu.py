@@ -41,6 +41,35 @@ def test_generic_kernels_match_oracle_and_golden(ma, case):
                 case["name"] + " vs reference golden")
 
 
+def _warp_ok(c):
+    M = -(-c["N"] // c["B"])
+    return (c["dtype"] in ("bf16", "f16") and c["vdtype"] == c["dtype"] and c["Dv"] == c["D"] and c["D"] % 8 == 0
+            and c["D"] <= 80 and c["B"] <= 128 and M <= 128)
+
+
+WARP_CASES = [c for c in CASES if _warp_ok(c)]
+
+
+@pytest.mark.parametrize("case", WARP_CASES, ids=[c["name"] for c in WARP_CASES])
+def test_warp_mma_kernels_match_oracle_and_golden(ma, case):
+    q, k, v, mask = make_inputs(case)
+    out = _run(ma, case, "b200-warp-mma", q, k, v, mask)
+    ref = monarch_attention_oracle(q, k, v, mask, case["T"], case["B"], case["pre_pad"])
+    vd = case["vdtype"]
+    check_close(out.double().cpu().numpy(), ref.double().numpy(), vd, case["name"] + " vs oracle")
+    check_close(bits_to_float(sample_of(out), vd), bits_to_float(golden_sample(case["name"]), vd), vd,
+                case["name"] + " vs reference golden")
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c["name"] for c in CASES])
+def test_default_kernel_choice_matches_oracle(ma, case):
+    """impl="b200": whichever family the library picks for the problem."""
+    q, k, v, mask = make_inputs(case)
+    out = _run(ma, case, "b200", q, k, v, mask)
+    ref = monarch_attention_oracle(q, k, v, mask, case["T"], case["B"], case["pre_pad"])
+    check_close(out.double().cpu().numpy(), ref.double().numpy(), case["vdtype"], case["name"] + " vs oracle")
+
+
 TC_CASES = [c for c in CASES if c["B"] == 128 and c["N"] == 16384 and c["dtype"] in ("bf16", "f16")]
 
 
@@ -89,7 +118,9 @@ def _state_from_workspace(ma, q, k, v, T, B, kernel):
 
 @pytest.mark.parametrize("name,kernel", [("cfg3_n16384_unit_bf16", 2), ("cfg3_n16384_unit_bf16", 3),
                                          ("cfg3_n16384_unit_bf16", 4), ("cfg3_n16384_unit_bf16", 1),
-                                         ("cfg3_n4096_unit_bf16", 1), ("edge_t4_f32", 1)])
+                                         ("cfg3_n4096_unit_bf16", 1), ("edge_t4_f32", 1),
+                                         ("cfg3_n4096_unit_bf16", 5), ("cfg3_n16384_unit_bf16", 5),
+                                         ("cfg5_dit_bf16", 5), ("edge_full_block_masked_t3_bf16", 5)])
 def test_stage_state_matches_oracle(ma, name, kernel):
     """Every stage-to-stage tensor (ar, cr, al, cl, y), not just the final output."""
     case = CASES_BY_NAME[name]
