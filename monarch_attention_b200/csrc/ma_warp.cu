@@ -82,18 +82,36 @@ __device__ __forceinline__ float quad_sum(float v) {
 
 // Copies `rows` rows of `width` 16-bit elements (width a multiple of 8) into a shared tile with row
 // pitch `pitch` elements, zero-filling rows whose source pointer is null, columns [width, wpad) and
-// rows [rows, rpad).  row_ptr(r) returns the global row or nullptr.
+// rows [rows, rpad).  row_ptr(r) returns the global row or nullptr.  Threads tid of nthreads cooperate
+// (a CTA works on several tiles at once, each with its own group of warps).
 template <typename T, typename RowFn>
-__device__ __forceinline__ void load_tile(T* tile, int pitch, int rows, int rpad, int width, int wpad, RowFn row_ptr) {
-  const int chunks = wpad >> 3;
-  for (int i = threadIdx.x; i < rpad * chunks; i += blockDim.x) {
-    const int r = i / chunks, c = (i - r * chunks) << 3;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (r < rows && c < width) {
-      const T* src = row_ptr(r);
-      if (src != nullptr) v = *reinterpret_cast<const uint4*>(src + c);
+__device__ __forceinline__ void load_tile(T* tile, int pitch, int rows, int rpad, int width, int wpad, RowFn row_ptr,
+                                          int tid, int nthreads) {
+  // four 16-byte loads are issued before the first of them is stored, so that each thread keeps
+  // several requests in flight (these kernels live on memory-level parallelism)
+  const int chunks = wpad >> 3, total = rpad * chunks;
+  for (int i0 = tid; i0 < total; i0 += 4 * nthreads) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + u * nthreads;
+      v[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (i < total) {
+        const int r = i / chunks, c = (i - r * chunks) << 3;
+        if (r < rows && c < width) {
+          const T* src = row_ptr(r);
+          if (src != nullptr) v[u] = *reinterpret_cast<const uint4*>(src + c);
+        }
+      }
     }
-    *reinterpret_cast<uint4*>(tile + r * pitch + c) = v;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + u * nthreads;
+      if (i < total) {
+        const int r = i / chunks, c = (i - r * chunks) << 3;
+        *reinterpret_cast<uint4*>(tile + r * pitch + c) = v[u];
+      }
+    }
   }
 }
 
