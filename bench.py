@@ -205,6 +205,91 @@ def run_reference(args, rank, world):
 
 
 # ---------------------------------------------------------------------------------------------
+# ViT-B/16 forward with MonarchAttention in every layer (second half of the headline metric)
+# ---------------------------------------------------------------------------------------------
+def build_vit_b(attn_factory, dtype, device):
+    """Plain-PyTorch ViT-B/16 (224x224x3 input, 196 patches + CLS, 12 pre-LN layers, hidden 768,
+    12 heads of 64, MLP 3072 with GELU), trunc-normal(0.02) random weights.  The attention call site is
+    the reference adapter's: q, k, v as permuted (E, H, N, D) views of the projection outputs,
+    ``attn_module(q, k, v)``, then ``permute(0, 2, 1, 3)`` back (reference: experiments/vit/model.py:73-103)."""
+    import torch.nn as nn
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.ln1, self.ln2 = nn.LayerNorm(768, eps=1e-12), nn.LayerNorm(768, eps=1e-12)
+            self.q, self.k, self.v, self.o = (nn.Linear(768, 768) for _ in range(4))
+            self.fc1, self.fc2 = nn.Linear(768, 3072), nn.Linear(3072, 768)
+            self.attn = attn_factory()
+
+        def forward(self, x):
+            E, N, _ = x.shape
+            hdn = self.ln1(x)
+            q, k, v = (p(hdn).view(E, N, 12, 64).permute(0, 2, 1, 3) for p in (self.q, self.k, self.v))
+            ctx = self.attn(q, k, v).permute(0, 2, 1, 3).contiguous().view(E, N, 768)
+            x = x + self.o(ctx)
+            return x + self.fc2(torch.nn.functional.gelu(self.fc1(self.ln2(x))))
+
+    class ViT(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.patch = nn.Conv2d(3, 768, 16, 16)
+            self.cls = nn.Parameter(torch.zeros(1, 1, 768))
+            self.pos = nn.Parameter(torch.zeros(1, 197, 768))
+            self.blocks = nn.ModuleList(Block() for _ in range(12))
+            self.ln = nn.LayerNorm(768, eps=1e-12)
+            self.head = nn.Linear(768, 1000)
+
+        def forward(self, img):
+            x = self.patch(img).flatten(2).transpose(1, 2)
+            x = torch.cat((self.cls.expand(x.shape[0], -1, -1), x), dim=1) + self.pos
+            for b in self.blocks:
+                x = b(x)
+            return self.head(self.ln(x)[:, 0])
+
+    torch.manual_seed(0)
+    model = ViT()
+    for p_ in model.parameters():
+        if p_.dim() > 1:
+            torch.nn.init.trunc_normal_(p_, std=0.02)
+    return model.to(device=device, dtype=dtype).eval()
+
+
+def time_vit(device, steps=10, warmup=3, batch=64):
+    """img/s of the ViT-B forward, bf16, batch 64, block size 15, one iteration, front padding; and the
+    same model with dense SDPA as context."""
+    from monarch_attention_b200 import MonarchAttention
+
+    class Dense(torch.nn.Module):
+        def forward(self, q, k, v):
+            return torch.nn.functional.scaled_dot_product_attention(q, k, v)
+
+    def monarch():
+        m = MonarchAttention(15, 1, "pre")
+        m.token_major_output = True
+        return m
+
+    g = torch.Generator(device="cpu").manual_seed(0)
+    img = torch.rand(batch, 3, 224, 224, generator=g).to(torch.bfloat16).to(device)
+    out = {}
+    for name, factory in (("monarch_b200", monarch), ("dense_sdpa", Dense)):
+        model = build_vit_b(factory, torch.bfloat16, device)
+        with torch.no_grad():
+            for _ in range(warmup):
+                model(img)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                logits = model(img)
+            e1.record()
+            torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        out[name] = {"img_per_s": batch / (ms * 1e-3), "ms_per_forward": ms, "finite": bool(torch.isfinite(logits).all())}
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
 # Our arm
 # ---------------------------------------------------------------------------------------------
 def run_ours(args, rank, world, local):
@@ -340,6 +425,12 @@ def run_ours(args, rank, world, local):
     except Exception as exc:  # context only
         context["dense_sdpa_ms"] = None
         context["dense_sdpa_error"] = str(exc)[:100]
+
+    # ---- second half of the headline metric: ViT-B/16 forward, img/s -----------------------------------
+    try:
+        context["vit_b16_bf16_batch64_b15_T1"] = time_vit(dev)
+    except Exception as exc:
+        context["vit_b16_error"] = str(exc)[:200]
 
     # ---- CPU baseline: the oracle port on the host cores, bounded sample ----------------------------
     cpu_baseline = None

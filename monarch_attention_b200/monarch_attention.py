@@ -106,18 +106,25 @@ def _mask_bytes(attn_mask: Tensor | None, device) -> Tensor | None:
 
 
 def monarch_attention_b200(q: Tensor, k: Tensor, v: Tensor, attn_mask: Tensor | None, T: int, B: int, pre_pad: bool,
-                           *, kernel: int = _cabi.KERNEL_AUTO, out: Tensor | None = None) -> Tensor:
+                           *, kernel: int = _cabi.KERNEL_AUTO, out: Tensor | None = None,
+                           token_major_output: bool = False) -> Tensor:
     """Implementation function with the reference's registry signature
     (reference: ma/monarch_attention.py:11-19; computes what ma/ma_torch.py:65-108 computes).
 
-    Returns a new (E, H, N, Dv) tensor of value's dtype on value's device.
+    Returns a new (E, H, N, Dv) tensor of value's dtype on value's device.  With
+    ``token_major_output`` the result is a (E, H, N, Dv) *view* of a (E, N, H, Dv) buffer, i.e. already
+    in the layout the model adapters produce with ``permute(0, 2, 1, 3).contiguous()`` after the call
+    (reference: experiments/vit/model.py:99-101), which then costs nothing.
     """
     _check_inputs(q, k, v, attn_mask)
     lib = _cabi.load()
     q, k, v = _unit_inner(q), _unit_inner(k), _unit_inner(v)
     E, H, N, _ = q.shape
     if out is None:
-        out = torch.empty((E, H, N, v.shape[-1]), dtype=v.dtype, device=v.device)
+        if token_major_output:
+            out = torch.empty((E, N, H, v.shape[-1]), dtype=v.dtype, device=v.device).permute(0, 2, 1, 3)
+        else:
+            out = torch.empty((E, H, N, v.shape[-1]), dtype=v.dtype, device=v.device)
     mask = _mask_bytes(attn_mask, q.device)
     prob = make_problem(q, k, v, out, mask, T, B, pre_pad, kernel)
     with torch.cuda.device(q.device):
@@ -178,8 +185,14 @@ class MonarchAttention(nn.Module):
             available = ", ".join(sorted(_IMPLEMENTATIONS))
             raise ValueError(f"Unknown impl {impl!r}. Available: {available}")
         self._impl_fn = _IMPLEMENTATIONS[impl]
+        # Set to True to get the result as a view of a (batch, tokens, heads, width) buffer (see
+        # monarch_attention_b200); only the default implementation honours it.
+        self.token_major_output = False
 
     def forward(self, query, key, value, attention_mask=None):
+        if self.token_major_output and self._impl_fn is monarch_attention_b200:
+            return monarch_attention_b200(query, key, value, attention_mask, self.num_steps, self.block_size,
+                                          self.pad_type == PadType.pre, token_major_output=True)
         return self._impl_fn(query, key, value, attention_mask, self.num_steps, self.block_size,
                              self.pad_type == PadType.pre)
 

@@ -161,6 +161,21 @@ def test_strided_views_are_read_in_place(ma):
     assert torch.equal(a, b)
 
 
+def test_token_major_output_is_the_adapter_layout(ma):
+    """The result as a view of a (E, N, H, D) buffer: the adapters' permute + contiguous becomes free
+    (reference: experiments/vit/model.py:99-101)."""
+    case = CASES_BY_NAME["cfg2_vit_bf16"]
+    q, k, v, _ = make_inputs(case)
+    dev = torch.device("cuda:0")
+    q, k, v = q.to(dev), k.to(dev), v.to(dev)
+    plain = ma.MonarchAttention(case["B"], case["T"], "pre")
+    tm = ma.MonarchAttention(case["B"], case["T"], "pre")
+    tm.token_major_output = True
+    a, b = plain(q, k, v), tm(q, k, v)
+    assert b.shape == a.shape and torch.equal(a, b)
+    assert b.permute(0, 2, 1, 3).is_contiguous() and not b.is_contiguous()
+
+
 def test_get_matrix_is_row_stochastic_and_matches_oracle(ma):
     case = CASES_BY_NAME["edge_matrix_f32v_bf16"]
     q, k, v, _ = make_inputs(case)
