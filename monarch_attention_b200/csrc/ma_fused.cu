@@ -60,6 +60,11 @@ constexpr int kThreads = 16 * 32;
 // three (A, B, V) - never wrapping: if the tail of the ring is too short it is skipped - so up to four
 // items of the two-tile kinds are in flight, which is what hides the latency of their loads.
 constexpr int kNumBarsConst = 32;
+// Tensor memory: three S accumulators (columns 0, 128, 256) so that S = A B^T of a group's next item
+// can run while the group is still reading its current one, and one O accumulator (column 384): the
+// epilogue empties it much faster than items arrive.
+constexpr int kSBuffers = 3;
+constexpr uint32_t kTmemO = 384;
 constexpr int kRingTiles = 9;
 constexpr int kItemsInFlight = 4;  // depth of the per-item barrier / row-vector rings
 constexpr uint32_t kOffSlots = 0;
@@ -76,12 +81,12 @@ constexpr uint32_t kSmemBytes = kSmemUsed + 1024;
 enum {
   kBarInFull = 0,    // [4] operand tiles of an item filled by TMA
   kBarInEmpty = 4,   // [4] operand tiles of an item released by the second contraction
-  kBarSFull = 8,     // [2] S accumulator ready
-  kBarSEmpty = 10,   // [2] S accumulator read by the softmax group
-  kBarPFull = 12,    // [2] P written
-  kBarPEmpty = 14,   // [2] P consumed by the second contraction
-  kBarOFull = 16,    // [2] O accumulator ready
-  kBarOEmpty = 18,   // [2] O accumulator read by the epilogue group
+  kBarSFull = 8,     // [3] S accumulator ready
+  kBarSEmpty = 11,   // [3] S accumulator read by the softmax group
+  kBarPFull = 14,    // [2] P written
+  kBarPEmpty = 16,   // [2] P consumed by the second contraction
+  kBarOFull = 18,    // [1] O accumulator ready
+  kBarOEmpty = 19,   // [1] O accumulator read by the epilogue group
   kBarDone = 20,     // [4] item stored to global memory by all 128 epilogue threads
   kBarPubFree = 24,  // [4] completion of that item published
   kBarStat = 28,     // [4] row statistics of the item written by its softmax group
@@ -204,13 +209,17 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
     static_assert(kNumBars == kNumBarsConst, "barrier count");
     for (int i = 0; i < kItemsInFlight; ++i) { mbar_init(bar(kBarInFull + i), 1); mbar_init(bar(kBarInEmpty + i), 1); }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(bar(kBarSFull + i), 1);
-      mbar_init(bar(kBarSEmpty + i), 128);
+
       mbar_init(bar(kBarPFull + i), 128);
       mbar_init(bar(kBarPEmpty + i), 1);
-      mbar_init(bar(kBarOFull + i), 1);
-      mbar_init(bar(kBarOEmpty + i), 128);
+
     }
+    for (int i = 0; i < kSBuffers; ++i) {
+      mbar_init(bar(kBarSFull + i), 1);
+      mbar_init(bar(kBarSEmpty + i), 128);
+    }
+    mbar_init(bar(kBarOFull), 1);
+    mbar_init(bar(kBarOEmpty), 128);
     for (int i = 0; i < 4; ++i) {
       mbar_init(bar(kBarDone + i), 128);
       mbar_init(bar(kBarStat + i), 128);
@@ -324,9 +333,9 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid(); cur.next(), ++n) {
         int t0, ntiles, skipped;
         (void)cur.take(&t0, &ntiles, &skipped);
-        const int slot = n % kItemsInFlight, sb = n & 1;
+        const int slot = n % kItemsInFlight, sb = n % kSBuffers;
         if (!mbar_wait_abortable(bar(kBarInFull + slot), (uint32_t)(n / kItemsInFlight) & 1u, abort_flag)) { give_up(301); break; }
-        if (!mbar_wait_abortable(bar(kBarSEmpty + sb), ((uint32_t)(n >> 1) & 1u) ^ 1u, abort_flag)) { give_up(302); break; }
+        if (!mbar_wait_abortable(bar(kBarSEmpty + sb), ((uint32_t)(n / kSBuffers) & 1u) ^ 1u, abort_flag)) { give_up(302); break; }
         tc_fence_after();
         if (!(dbg_flags & 8)) {
           const uint32_t dA = dA0 + t0 * kTileStep, dB = dA + kTileStep;
@@ -352,13 +361,13 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         const int pb = n & 1, slot = n % kItemsInFlight;
         const uint32_t ph2 = (uint32_t)(n >> 1) & 1u;
         if (!mbar_wait_abortable(bar(kBarPFull + pb), ph2, abort_flag)) { give_up(303); break; }
-        if (!mbar_wait_abortable(bar(kBarOEmpty + pb), ph2 ^ 1u, abort_flag)) { give_up(304); break; }
+        if (!mbar_wait_abortable(bar(kBarOEmpty), ((uint32_t)n & 1u) ^ 1u, abort_flag)) { give_up(304); break; }
         tc_fence_after();
         if (!(dbg_flags & 8)) {
           const uint32_t dPk = dP_k0 + pb * kPStep, dPmn = dP_mn0 + pb * kPStep;
           // tiles of the item: A (left stage: q' written over it), B, V
           const uint32_t dA = dTmn0 + t0 * kTileStep, dB = dA + kTileStep, dV = dB + kTileStep;
-          const uint32_t tmem_o = tmem + 256 + pb * 128;
+          const uint32_t tmem_o = tmem + kTmemO;
           if (kind == kStageRight) {
             constexpr uint32_t idesc = instr_desc(kFmt, 0, 1, kHead, kTile);
 #pragma unroll
@@ -386,7 +395,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
               mma_f16_lo(tmem_o, dPk + ((kk >> 2) * kTileStep + (kk & 3) * 2), dV + kk * 128, idesc, kk > 0);
           }
         }
-        mma_commit(bar(kBarOFull + pb));
+        mma_commit(bar(kBarOFull));
         mma_commit(bar(kBarPEmpty + pb));
         mma_commit(bar(kBarInEmpty + slot));
       }
@@ -418,16 +427,15 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
     ItemCursor cur;
     for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid(); cur.next(), ++n) {
       const Item it = cur.get();
-      const int ob = n & 1;
       if (!mbar_wait_abortable(bar(kBarStat + (n & 3)), (uint32_t)(n >> 2) & 1u, abort_flag) ||
-          !mbar_wait_abortable(bar(kBarOFull + ob), (uint32_t)(n >> 1) & 1u, abort_flag)) {
+          !mbar_wait_abortable(bar(kBarOFull), (uint32_t)n & 1u, abort_flag)) {
         give_up(501);
         break;
       }
       tc_fence_after();
       const float* stp = reinterpret_cast<const float*>(base_ptr + kOffStats) + ((n & 3) * 128 + row) * 3;
       const float4 st = make_float4(stp[0], stp[1], stp[2], 0.f);
-      const uint32_t tmem_o = tmem + lane_base + 256 + ob * 128;
+      const uint32_t tmem_o = tmem + lane_base + kTmemO;
       T* dst0;
       if (it.kind == kStageRight || it.kind == kStageRightWithV) {
         dst0 = reinterpret_cast<T*>(g.al) + (((long long)it.eh * g.B + row) * g.M + it.tile) * kHead;
@@ -468,7 +476,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         }
       }
       tc_fence_before();
-      mbar_arrive(bar(kBarOEmpty + ob));
+      mbar_arrive(bar(kBarOEmpty));
       if (args.wait_deps) {
         // hand the item to the publisher warp (4-deep ring)
         if (!mbar_wait_abortable(bar(kBarPubFree + (n & 3)), ((uint32_t)(n >> 2) & 1u) ^ 1u, abort_flag)) {
@@ -500,7 +508,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       const Item it = cur.take(&tile0, &ntiles, &skipped);  // every item moves the ring position
       if ((n & 1) != grp) continue;
       MA_TR(0)
-      const int slot = n % kItemsInFlight, sb = n & 1;
+      const int slot = n % kItemsInFlight, sb = n & 1, s3 = n % kSBuffers;  // P buffer / S accumulator of the item
       const uint32_t ph2 = (uint32_t)(n >> 1) & 1u;
       const bool right = it.kind == kStageRight || it.kind == kStageRightWithV;
       const uint32_t sA = base + kOffSlots + tile0 * kTileBytes;
@@ -508,10 +516,10 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       const float* vec = reinterpret_cast<const float*>(base_ptr + kOffVec + slot * 512);
 
       if (!mbar_wait_abortable(bar(kBarInFull + slot), (uint32_t)(n / kItemsInFlight) & 1u, abort_flag)) { give_up(401); alive = false; break; }
-      if (!mbar_wait_abortable(bar(kBarSFull + sb), ph2, abort_flag)) { give_up(402); alive = false; break; }
+      if (!mbar_wait_abortable(bar(kBarSFull + s3), (uint32_t)(n / kSBuffers) & 1u, abort_flag)) { give_up(402); alive = false; break; }
       tc_fence_after();
       MA_TR(1)
-      const uint32_t tmem_s = tmem + lane_base + sb * 128;
+      const uint32_t tmem_s = tmem + lane_base + s3 * 128;
 
       // Two passes over the row of S, each a short loop over 64-column halves whose body handles two
       // 32-column chunks in two register buffers: the tensor-memory load of the next chunk is in flight
@@ -579,7 +587,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           tmem_wait_ld(ca); tmem_ld32_nowait(tmem_s + 64 * h + 32, cb); exp_chunk(ca, 64 * h);
           tmem_wait_ld(cb);
           if (h == 0) tmem_ld32_nowait(tmem_s + 64, ca);
-          else { tc_fence_before(); mbar_arrive(bar(kBarSEmpty + sb)); }  // S has been read in full
+          else { tc_fence_before(); mbar_arrive(bar(kBarSEmpty + s3)); }  // S has been read in full
           exp_chunk(cb, 64 * h + 32);
         }
       } else {
@@ -625,7 +633,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           tmem_wait_ld(ca); tmem_ld32_nowait(tmem_s + 64 * h + 32, cb); exp_chunk(ca, vec + 64 * h, 64 * h);
           tmem_wait_ld(cb);
           if (h == 0) tmem_ld32_nowait(tmem_s + 64, ca);
-          else { tc_fence_before(); mbar_arrive(bar(kBarSEmpty + sb)); }  // S has been read in full
+          else { tc_fence_before(); mbar_arrive(bar(kBarSEmpty + s3)); }  // S has been read in full
           exp_chunk(cb, vec + 64 * h + 32, 64 * h + 32);
         }
       }
