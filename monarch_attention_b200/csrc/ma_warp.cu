@@ -82,37 +82,27 @@ __device__ __forceinline__ float quad_sum(float v) {
 
 // Copies `rows` rows of `width` 16-bit elements (width a multiple of 8) into a shared tile with row
 // pitch `pitch` elements, zero-filling rows whose source pointer is null, columns [width, wpad) and
-// rows [rows, rpad).  row_ptr(r) returns the global row or nullptr.  Threads tid of nthreads cooperate
-// (a CTA works on several tiles at once, each with its own group of warps).
+// rows [rows, rpad).  row_ptr(r) returns the global row or nullptr.  Threads tid of nthreads cooperate.
+// The copies are asynchronous (cp.async, 16 bytes each, zero-fill by giving a source size of 0): a
+// thread queues all of its pieces without waiting, which is what keeps enough bytes in flight for
+// these memory-bound kernels; tiles_commit_and_wait() must be called before the tile is read.
 template <typename T, typename RowFn>
 __device__ __forceinline__ void load_tile(T* tile, int pitch, int rows, int rpad, int width, int wpad, RowFn row_ptr,
-                                          int tid, int nthreads) {
-  // four 16-byte loads are issued before the first of them is stored, so that each thread keeps
-  // several requests in flight (these kernels live on memory-level parallelism)
+                                          int tid, int nthreads, const void* any_valid_global) {
   const int chunks = wpad >> 3, total = rpad * chunks;
-  for (int i0 = tid; i0 < total; i0 += 4 * nthreads) {
-    uint4 v[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int i = i0 + u * nthreads;
-      v[u] = make_uint4(0u, 0u, 0u, 0u);
-      if (i < total) {
-        const int r = i / chunks, c = (i - r * chunks) << 3;
-        if (r < rows && c < width) {
-          const T* src = row_ptr(r);
-          if (src != nullptr) v[u] = *reinterpret_cast<const uint4*>(src + c);
-        }
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int i = i0 + u * nthreads;
-      if (i < total) {
-        const int r = i / chunks, c = (i - r * chunks) << 3;
-        *reinterpret_cast<uint4*>(tile + r * pitch + c) = v[u];
-      }
-    }
+  for (int i = tid; i < total; i += nthreads) {
+    const int r = i / chunks, c = (i - r * chunks) << 3;
+    const T* src = (r < rows && c < width) ? row_ptr(r) : nullptr;
+    const void* gsrc = src != nullptr ? static_cast<const void*>(src + c) : any_valid_global;
+    const uint32_t nbytes = src != nullptr ? 16u : 0u;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(tile + r * pitch + c)), "l"(gsrc),
+                 "r"(nbytes)
+                 : "memory");
   }
+}
+__device__ __forceinline__ void tiles_commit_and_wait() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
 __device__ __forceinline__ bool pos_valid(const Geometry& g, int e, int p) {
