@@ -53,20 +53,23 @@ enum {
 enum { MA_B200_F32 = 0, MA_B200_BF16 = 1, MA_B200_F16 = 2 };
 
 /* Kernel families.  AUTO picks the fused tcgen05 kernel when the problem fits it, else the
- * warp-level tensor-core kernels when they fit, else the generic kernels.
+ * warp-level tensor-core kernels, else the generic kernels.
  *   GENERIC        SIMT stage kernels, any shape / dtype / mask (2T launches)
  *   TCGEN05        persistent tcgen05 kernel, all 2T stages in one launch
  *   TCGEN05_STAGED the same kernel launched once per stage (for per-stage timing)
  *   TCGEN05_TILE   one-tile-per-CTA tcgen05 stage kernels (2T launches; cross-check)
  *   WARP_MMA       warp-level tensor-core stage kernels for 16-bit inputs with block size and
- *                  block count up to 128 and D <= 80 (2T launches; masks and padding handled) */
+ *                  block count up to 128 and D <= 80 (2T launches; masks and padding handled)
+ *   HEAD_FUSED     one CTA per head, one iteration (T = 1), block size and count <= 32, D <= 64:
+ *                  both stages in one launch with al, y, cl in shared memory (1 launch) */
 enum {
   MA_B200_KERNEL_AUTO = 0,
   MA_B200_KERNEL_GENERIC = 1,
   MA_B200_KERNEL_TCGEN05 = 2,
   MA_B200_KERNEL_TCGEN05_STAGED = 3,
   MA_B200_KERNEL_TCGEN05_TILE = 4,
-  MA_B200_KERNEL_WARP_MMA = 5
+  MA_B200_KERNEL_WARP_MMA = 5,
+  MA_B200_KERNEL_HEAD_FUSED = 6
 };
 
 typedef struct ma_b200_tensor {

@@ -10,10 +10,10 @@ import os
 
 ABI_VERSION = 1
 F32, BF16, F16 = 0, 1, 2
-KERNEL_AUTO, KERNEL_GENERIC, KERNEL_TCGEN05, KERNEL_TCGEN05_STAGED, KERNEL_TCGEN05_TILE, KERNEL_WARP_MMA = 0, 1, 2, 3, 4, 5
+KERNEL_AUTO, KERNEL_GENERIC, KERNEL_TCGEN05, KERNEL_TCGEN05_STAGED, KERNEL_TCGEN05_TILE, KERNEL_WARP_MMA, KERNEL_HEAD_FUSED = 0, 1, 2, 3, 4, 5, 6
 KERNEL_NAMES = {KERNEL_AUTO: "auto", KERNEL_GENERIC: "generic", KERNEL_TCGEN05: "tcgen05-fused",
                 KERNEL_TCGEN05_STAGED: "tcgen05-staged", KERNEL_TCGEN05_TILE: "tcgen05-tile",
-                KERNEL_WARP_MMA: "warp-mma"}
+                KERNEL_WARP_MMA: "warp-mma", KERNEL_HEAD_FUSED: "head-fused"}
 OK, INVALID_ARGUMENT, UNSUPPORTED, CUDA_ERROR, DEVICE_WAIT_EXPIRED, WORKSPACE_TOO_SMALL = range(6)
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libmonarch_attention_b200.so")

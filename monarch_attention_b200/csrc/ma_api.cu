@@ -41,7 +41,7 @@ int validate(const ma_b200_problem* p, bool need_pointers) {
     return fail(MA_B200_INVALID_ARGUMENT, "unknown dtype");
   if (!(p->qk_dtype == p->v_dtype || p->v_dtype == MA_B200_F32))
     return fail(MA_B200_UNSUPPORTED, "v_dtype must equal qk_dtype or be f32");
-  if (p->kernel < MA_B200_KERNEL_AUTO || p->kernel > MA_B200_KERNEL_WARP_MMA)
+  if (p->kernel < MA_B200_KERNEL_AUTO || p->kernel > MA_B200_KERNEL_HEAD_FUSED)
     return fail(MA_B200_INVALID_ARGUMENT, "unknown kernel family");
   if ((long long)p->E * p->H > 0x7fffffffLL / 2) return fail(MA_B200_INVALID_ARGUMENT, "E*H too large");
   if (need_pointers) {
@@ -93,7 +93,13 @@ int resolve_kernel(const ma_b200_problem* p, const ma::Geometry& g, int* kernel)
   const bool warp_ok = ma::warp_supported(g, p->qk_dtype, p->v_dtype, &why_w);
   if (p->kernel == MA_B200_KERNEL_WARP_MMA && !warp_ok)
     return fail(MA_B200_UNSUPPORTED, std::string("warp-level tensor-core path cannot run this problem: ") + why_w);
+  const char* why_h = "";
+  const bool head_ok = ma::head_fused_supported(g, p->qk_dtype, p->v_dtype, &why_h);
+  if (p->kernel == MA_B200_KERNEL_HEAD_FUSED && !head_ok)
+    return fail(MA_B200_UNSUPPORTED, std::string("one-CTA-per-head kernel cannot run this problem: ") + why_h);
   if (p->kernel == MA_B200_KERNEL_AUTO)
+    // (the one-CTA-per-head kernel is selectable but not preferred: on the ViT / RoBERTa shapes it
+    // measured slower than the two staged launches - these tiny tiles are instruction-bound)
     *kernel = tc_ok ? MA_B200_KERNEL_TCGEN05 : (warp_ok ? MA_B200_KERNEL_WARP_MMA : MA_B200_KERNEL_GENERIC);
   else *kernel = p->kernel;
   if (*kernel == MA_B200_KERNEL_GENERIC) {
@@ -189,7 +195,12 @@ int run_forward(const ma_b200_problem* p, void* workspace, size_t workspace_byte
 
   rc = MA_B200_OK;
   bool first = true;
-  if (L.kernel == MA_B200_KERNEL_TCGEN05) {
+  if (L.kernel == MA_B200_KERNEL_HEAD_FUSED) {
+    ce = ma::launch_head_fused(g, p->qk_dtype, stream);
+    if (ce != cudaSuccess) rc = cuda_fail(ce, "one-CTA-per-head kernel");
+    if (ev != nullptr)
+      for (int i = 1; i <= n_stages; ++i) cudaEventRecord(ev[i], stream);
+  } else if (L.kernel == MA_B200_KERNEL_TCGEN05) {
     // every stage in one persistent launch
     ce = ma::launch_fused(plan, g, counters, 0, n_stages, 1, stream);
     if (ce != cudaSuccess) rc = cuda_fail(ce, "fused kernel");

@@ -74,6 +74,9 @@ size_t generic_stage_smem_bytes(const Geometry& g, StageKind kind);
 // Warp-level tensor-core stage kernels (16-bit, block size and count <= 128, D <= 80).
 bool warp_supported(const Geometry& g, int qk_dtype, int v_dtype, const char** why);
 cudaError_t launch_warp_stage(const Geometry& g, int qk_dtype, StageKind kind, bool first, cudaStream_t stream);
+// Whole head per CTA, both stages of a one-iteration call in one launch (state in shared memory).
+bool head_fused_supported(const Geometry& g, int qk_dtype, int v_dtype, const char** why);
+cudaError_t launch_head_fused(const Geometry& g, int qk_dtype, cudaStream_t stream);
 
 // Tensor-core (tcgen05) path.
 bool tc_supported(const Geometry& g, int qk_dtype, int v_dtype, const char** why);

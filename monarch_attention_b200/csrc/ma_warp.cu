@@ -110,11 +110,16 @@ __device__ __forceinline__ bool pos_valid(const Geometry& g, int e, int p) {
   if (n < 0 || n >= g.N) return false;
   return g.mask == nullptr || g.mask[(long long)e * g.mask_se + n] != 0;
 }
+// Row of a user tensor for padded position p, given the (e, h) base pointer: nullptr for padding.
 template <typename T>
-__device__ __forceinline__ const T* user_row(const View4& t, int e, int h, int p, const Geometry& g) {
+__device__ __forceinline__ const T* head_base(const View4& t, int e, int h) {
+  return reinterpret_cast<const T*>(t.ptr) + (long long)e * t.se + (long long)h * t.sh;
+}
+template <typename T>
+__device__ __forceinline__ const T* user_row(const T* base, long long sn, int p, const Geometry& g) {
   const int n = p - g.pad_off;
   if (n < 0 || n >= g.N) return nullptr;
-  return reinterpret_cast<const T*>(t.ptr) + (long long)e * t.se + (long long)h * t.sh + (long long)n * t.sn;
+  return base + (long long)n * sn;
 }
 
 }  // namespace

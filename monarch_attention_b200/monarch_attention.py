@@ -161,6 +161,8 @@ register_impl("b200-tcgen05-staged",
               lambda q, k, v, m, T, B, pp: monarch_attention_b200(q, k, v, m, T, B, pp, kernel=_cabi.KERNEL_TCGEN05_STAGED))
 register_impl("b200-warp-mma",
               lambda q, k, v, m, T, B, pp: monarch_attention_b200(q, k, v, m, T, B, pp, kernel=_cabi.KERNEL_WARP_MMA))
+register_impl("b200-head-fused",
+              lambda q, k, v, m, T, B, pp: monarch_attention_b200(q, k, v, m, T, B, pp, kernel=_cabi.KERNEL_HEAD_FUSED))
 register_impl("b200-tcgen05-tile",
               lambda q, k, v, m, T, B, pp: monarch_attention_b200(q, k, v, m, T, B, pp, kernel=_cabi.KERNEL_TCGEN05_TILE))
 
@@ -171,7 +173,8 @@ class MonarchAttention(nn.Module):
     ``impl`` selects the kernel family: "b200" (default: fused tensor-core kernel when the
     problem fits it, otherwise the generic path), "b200-generic", "b200-tcgen05" (fused, one
     launch), "b200-tcgen05-staged" (same kernel, one launch per stage), "b200-tcgen05-tile"
-    (one tile per CTA) or "b200-warp-mma" (warp-level tensor-core kernels for small blocks).  The reference's
+    (one tile per CTA), "b200-warp-mma" (warp-level tensor-core kernels for small blocks) or
+    "b200-head-fused" (one CTA per head, one iteration, state in shared memory).  The reference's
     "torch" and "triton" implementations are not part of this library; asking for an
     unknown name raises ``ValueError`` exactly as the reference does.
     """
