@@ -1,10 +1,11 @@
 // Warp-level tensor-core stage kernels for 16-bit inputs with block size and block count up to 128:
 // the ViT / RoBERTa / DiT shapes (b = 14..32, N <= 1024, D = 64 or 72) and the b = 64 op sweep.
 //
-// These shapes are HBM-bound (intensity ~1.25*b FLOP/B) and their blocks are far smaller than a
-// tcgen05 tile, so the job here is to move each operand once, with every row masked / zero-padded in
+// By bytes these shapes are HBM-bound (intensity ~1.25*b FLOP/B) and their blocks are far smaller than
+// a tcgen05 tile, so the job here is to move each operand once, with every row masked / zero-padded in
 // flight, and to keep the small contractions on tensor cores: mma.sync m16n8k16 with fp32
-// accumulation, fragments read from padded shared-memory tiles with ldmatrix.  One CTA works on one
+// accumulation, fragments read from padded shared-memory tiles with ldmatrix.  Measured, the tiles
+// are so small that instruction issue (address arithmetic, softmax, staging) is what bounds them.  One CTA works on one
 // tile - (head, key block m) for the right-factor stages, (head, column j) for the left-factor and
 // output stages - with one warp per 16 rows.  The row softmax runs on the accumulator fragments
 // (a row lives in one quad of lanes), and the normalised factor goes back into the second
@@ -84,8 +85,8 @@ __device__ __forceinline__ float quad_sum(float v) {
 // pitch `pitch` elements, zero-filling rows whose source pointer is null, columns [width, wpad) and
 // rows [rows, rpad).  row_ptr(r) returns the global row or nullptr.  Threads tid of nthreads cooperate.
 // The copies are asynchronous (cp.async, 16 bytes each, zero-fill by giving a source size of 0): a
-// thread queues all of its pieces without waiting, which is what keeps enough bytes in flight for
-// these memory-bound kernels; tiles_commit_and_wait() must be called before the tile is read.
+// thread queues all of its pieces without waiting, which keeps many bytes in flight per thread;
+// tiles_commit_and_wait() must be called before the tile is read.
 template <typename T, typename RowFn>
 __device__ __forceinline__ void load_tile(T* tile, int pitch, int rows, int rpad, int width, int wpad, RowFn row_ptr,
                                           int tid, int nthreads, const void* any_valid_global) {
@@ -125,4 +126,7 @@ __device__ __forceinline__ const T* user_row(const T* base, long long sn, int p,
 }  // namespace
 }  // namespace ma
 
+// Explicit launcher templates are declared before use in ma_warp_kernels.inc and defined in
+// ma_warp_wide.inc, so the public entry points have to come last.
 #include "ma_warp_kernels.inc"
+#include "ma_warp_wide.inc"

@@ -79,6 +79,8 @@ def _config_cases():
         _c("cfg3_n16384_unit_bf16", 1, 1, 16384, 64, 128, 2, False, "bf16", scale="unit"),
         _c("cfg3_n4096_f16", 1, 1, 4096, 64, 64, 2, False, "f16", scale="unit"),
         _c("cfg3_n4096_f32", 1, 1, 4096, 64, 64, 2, False, "f32", scale="unit"),
+        _c("cfg3_n65536_bf16", 1, 1, 65536, 64, 256, 2, False, "bf16", scale="activations"),
+        _c("cfg3_n65536_unit_f16", 1, 1, 65536, 64, 256, 2, False, "f16", scale="unit"),
         # config 4 (RoBERTa): right padding produces fully masked key blocks
         _c("cfg4_roberta_bf16", 4, 12, 512, 64, 32, 1, False, "bf16", mask="right_pad", scale="activations"),
         _c("cfg4_roberta_t2_f32", 4, 2, 512, 64, 32, 2, False, "f32", mask="right_pad", scale="activations"),
@@ -107,6 +109,10 @@ def _edge_cases():
         _c("edge_large_logits_f32", 1, 2, 64, 32, 8, 2, False, "f32", scale="large"),
         _c("edge_t4_f32", 1, 2, 64, 16, 8, 4, False, "f32"),
         _c("edge_b1_f32", 1, 1, 8, 16, 1, 2, False, "f32"),
+        # block size and / or block count between 129 and 256, ragged, masked
+        _c("edge_b200_m150_mask_bf16", 1, 2, 200 * 150 - 37, 64, 200, 2, True, "bf16", mask="block_safe"),
+        _c("edge_b136_m40_f16", 2, 1, 136 * 40 - 5, 32, 136, 3, False, "f16", scale="rsqrt_d"),
+        _c("edge_b24_m200_bf16", 1, 2, 24 * 200 - 3, 64, 24, 2, False, "bf16", mask="right_pad_short"),
         _c("edge_n1_f32", 1, 1, 1, 16, 4, 2, True, "f32"),
     ]
 

@@ -44,7 +44,7 @@ def test_generic_kernels_match_oracle_and_golden(ma, case):
 def _warp_ok(c):
     M = -(-c["N"] // c["B"])
     return (c["dtype"] in ("bf16", "f16") and c["vdtype"] == c["dtype"] and c["Dv"] == c["D"] and c["D"] % 8 == 0
-            and c["D"] <= 80 and c["B"] <= 128 and M <= 128)
+            and c["D"] <= 80 and c["B"] <= 256 and M <= 256 and (c["D"] <= 64 or max(c["B"], M) <= 128))
 
 
 WARP_CASES = [c for c in CASES if _warp_ok(c)]
@@ -142,7 +142,8 @@ def _state_from_workspace(ma, q, k, v, T, B, kernel):
                                          ("cfg3_n16384_unit_bf16", 4), ("cfg3_n16384_unit_bf16", 1),
                                          ("cfg3_n4096_unit_bf16", 1), ("edge_t4_f32", 1),
                                          ("cfg3_n4096_unit_bf16", 5), ("cfg3_n16384_unit_bf16", 5),
-                                         ("cfg5_dit_bf16", 5), ("edge_full_block_masked_t3_bf16", 5)])
+                                         ("cfg5_dit_bf16", 5), ("edge_full_block_masked_t3_bf16", 5),
+                                         ("cfg3_n65536_bf16", 5), ("edge_b136_m40_f16", 5)])
 def test_stage_state_matches_oracle(ma, name, kernel):
     """Every stage-to-stage tensor (ar, cr, al, cl, y), not just the final output."""
     case = CASES_BY_NAME[name]
