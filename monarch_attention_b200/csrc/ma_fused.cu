@@ -74,7 +74,9 @@ constexpr uint32_t kOffVec = kOffSv + 2 * 4096;                  // 4 x 512 B (p
 static_assert(kOffP % 1024 == 0 && kOffSv % 1024 == 0, "swizzled operands need 1024-byte alignment");
 constexpr uint32_t kOffStats = kOffVec + kItemsInFlight * 512;   // 4 x 128 x 3 floats of row statistics
 constexpr uint32_t kOffBar = kOffStats + 4 * 128 * 12;
-constexpr uint32_t kSmemUsed = kOffBar + 8 * kNumBarsConst + 16;
+constexpr int kDescRing = 16;  // item descriptors; deeper than the producer can run ahead of the publisher (9)
+constexpr uint32_t kOffDesc = kOffBar + 8 * kNumBarsConst + 16;
+constexpr uint32_t kSmemUsed = kOffDesc + 8 * kDescRing;
 constexpr uint32_t kSmemBytes = kSmemUsed + 1024;
 
 // mbarrier indices (8 bytes each)
@@ -245,6 +247,21 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
+  // Only the producer walks the item schedule.  It leaves a two-word descriptor per item in a small
+  // ring (written before the arrive that opens the item's operand barrier, so every later hand-off
+  // carries it); the other roles read it once their first wait for the item has returned.
+  const int n_items = total > (int)blockIdx.x ? (total - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  auto read_item = [&](int n, int* first_tile) {
+    const int2 d = *reinterpret_cast<const int2*>(base_ptr + kOffDesc + (n & (kDescRing - 1)) * 8);
+    Item it;
+    it.kind = d.x & 3;
+    it.first = (d.x >> 2) & 1;
+    *first_tile = (d.x >> 3) & 15;
+    it.tile = (d.x >> 8) & 255;
+    it.stage = d.x >> 16;
+    it.eh = d.y;
+    return it;
+  };
   auto give_up = [&](int code) {
     *abort_flag = 1;
     atomicCAS(g.status, 0, code);
@@ -299,6 +316,8 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         const bool right = it.kind == kStageRight || it.kind == kStageRightWithV;
         const bool three = ntiles == 3;
         const bool has_vec = !(right && it.first);
+        *reinterpret_cast<int2*>(base_ptr + kOffDesc + (n & (kDescRing - 1)) * 8) =
+            make_int2(it.kind | (it.first << 2) | (t0 << 3) | (it.tile << 8) | (it.stage << 16), it.eh);
         mbar_expect_tx(full, (three ? 3u : 2u) * kTileBytes + (has_vec ? 512u : 0u));
         if (right) {
           if (it.first) tma_load_5d(sA, &maps.q_blk, full, 0, 0, it.tile, h, e);
@@ -328,13 +347,11 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       const uint32_t dA0 = smem_desc_lo(base + kOffSlots, 16);  // ring tile 0 as a K-major operand; B follows A
       constexpr uint32_t kTileStep = kTileBytes >> 4;
       constexpr uint32_t idesc1 = instr_desc(kFmt, 0, 0, kTile, kTile);
-      int n = 0;
-      ItemCursor cur;
-      for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid(); cur.next(), ++n) {
-        int t0, ntiles, skipped;
-        (void)cur.take(&t0, &ntiles, &skipped);
+      for (int n = 0; n < n_items; ++n) {
         const int slot = n % kItemsInFlight, sb = n % kSBuffers;
         if (!mbar_wait_abortable(bar(kBarInFull + slot), (uint32_t)(n / kItemsInFlight) & 1u, abort_flag)) { give_up(301); break; }
+        int t0;
+        (void)read_item(n, &t0);
         if (!mbar_wait_abortable(bar(kBarSEmpty + sb), ((uint32_t)(n / kSBuffers) & 1u) ^ 1u, abort_flag)) { give_up(302); break; }
         tc_fence_after();
         if (!(dbg_flags & 8)) {
@@ -353,14 +370,12 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       const uint32_t dS0 = smem_desc_lo(base + kOffSv, 16);             // 16 x 128 K-major operand (1/rowsum)
       const uint32_t dTmn0 = smem_desc_lo(base + kOffSlots, kTileBytes);  // ring tile 0 as an MN-major operand
       constexpr uint32_t kTileStep = kTileBytes >> 4, kPStep = (2 * kTileBytes) >> 4;
-      int n = 0;
-      ItemCursor cur;
-      for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid(); cur.next(), ++n) {
-        int t0, ntiles, skipped;
-        const int kind = cur.take(&t0, &ntiles, &skipped).kind;
+      for (int n = 0; n < n_items; ++n) {
         const int pb = n & 1, slot = n % kItemsInFlight;
         const uint32_t ph2 = (uint32_t)(n >> 1) & 1u;
         if (!mbar_wait_abortable(bar(kBarPFull + pb), ph2, abort_flag)) { give_up(303); break; }
+        int t0;
+        const int kind = read_item(n, &t0).kind;
         if (!mbar_wait_abortable(bar(kBarOEmpty), ((uint32_t)n & 1u) ^ 1u, abort_flag)) { give_up(304); break; }
         tc_fence_after();
         if (!(dbg_flags & 8)) {
@@ -405,11 +420,10 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
     // Makes the stores of every finished item visible device-wide and counts the item in its
     // (head, stage) completion counter, off the critical path of the epilogue group.
     if (lane == 0 && args.wait_deps) {
-      int n = 0;
-      ItemCursor cur;
-      for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid(); cur.next(), ++n) {
-        const Item it = cur.get();
+      for (int n = 0; n < n_items; ++n) {
         if (!mbar_wait_abortable(bar(kBarDone + (n & 3)), (uint32_t)(n >> 2) & 1u, abort_flag)) { give_up(601); break; }
+        int t0;
+        const Item it = read_item(n, &t0);
         if (it.stage != nst_all - 1) {  // nothing consumes the output stage
           __threadfence();
           atomicAdd(args.counters + it.eh * nst_all + it.stage, 1);
@@ -423,16 +437,15 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
     // =========================== epilogue group =================================================
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    int n = 0;
-    ItemCursor cur;
-    for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid(); cur.next(), ++n) {
-      const Item it = cur.get();
+    for (int n = 0; n < n_items; ++n) {
       if (!mbar_wait_abortable(bar(kBarStat + (n & 3)), (uint32_t)(n >> 2) & 1u, abort_flag) ||
           !mbar_wait_abortable(bar(kBarOFull), (uint32_t)n & 1u, abort_flag)) {
         give_up(501);
         break;
       }
       tc_fence_after();
+      int t0_unused;
+      const Item it = read_item(n, &t0_unused);
       const float* stp = reinterpret_cast<const float*>(base_ptr + kOffStats) + ((n & 3) * 128 + row) * 3;
       const float4 st = make_float4(stp[0], stp[1], stp[2], 0.f);
       const uint32_t tmem_o = tmem + lane_base + kTmemO;
@@ -492,7 +505,6 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
     const int grp = warp >> 2;                      // items with local index n = grp (mod 2)
     const int row = (warp & 3) * 32 + lane;         // tensor-memory lane = tile row
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    int n = 0;
     bool alive = true;
 #if defined(MA_DIAG) && defined(MA_TRACE)
     long long tr[8][8];
@@ -502,20 +514,19 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
 #else
 #define MA_TR(i)
 #endif
-    ItemCursor cur;
-    for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid(); cur.next(), ++n) {
-      int tile0, ntiles, skipped;
-      const Item it = cur.take(&tile0, &ntiles, &skipped);  // every item moves the ring position
-      if ((n & 1) != grp) continue;
+    int n = grp;
+    for (; n < n_items; n += 2) {
       MA_TR(0)
       const int slot = n % kItemsInFlight, sb = n & 1, s3 = n % kSBuffers;  // P buffer / S accumulator of the item
       const uint32_t ph2 = (uint32_t)(n >> 1) & 1u;
-      const bool right = it.kind == kStageRight || it.kind == kStageRightWithV;
-      const uint32_t sA = base + kOffSlots + tile0 * kTileBytes;
       const uint32_t sP = base + kOffP + sb * 2 * kTileBytes;
       const float* vec = reinterpret_cast<const float*>(base_ptr + kOffVec + slot * 512);
 
       if (!mbar_wait_abortable(bar(kBarInFull + slot), (uint32_t)(n / kItemsInFlight) & 1u, abort_flag)) { give_up(401); alive = false; break; }
+      int tile0;
+      const Item it = read_item(n, &tile0);
+      const bool right = it.kind == kStageRight || it.kind == kStageRightWithV;
+      const uint32_t sA = base + kOffSlots + tile0 * kTileBytes;
       if (!mbar_wait_abortable(bar(kBarSFull + s3), (uint32_t)(n / kSBuffers) & 1u, abort_flag)) { give_up(402); alive = false; break; }
       tc_fence_after();
       MA_TR(1)
@@ -643,11 +654,12 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       float4 st = make_float4(0.f, 0.f, 0.f, 0.f);  // scale of O[:, :64], scale of O[:, 64:], cl, unused
       if (right) {
         const float denom = row_sum + kEps;
-        st.x = g.sm_scale / denom;
-        st.y = 1.0f / denom;
-        st.z = (kLn2 * row_ent) / denom - logf(denom) * (row_sum / denom);
+        const float rden = __frcp_rn(denom);
+        st.x = g.sm_scale * rden;
+        st.y = rden;
+        st.z = kLn2 * (row_ent - __log2f(denom) * row_sum) * rden;
       } else if (it.kind == kStageLeft) {
-        const float inv = 1.0f / row_sum;
+        const float inv = __frcp_rn(row_sum);
         st.x = 1.0f;
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {  // q' = q / rowsum, in place (S = A B^T has consumed the tile)
@@ -659,7 +671,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         T* srow = reinterpret_cast<T*>(base_ptr + kOffSv + sb * 4096 + (row >> 6) * 2048);
         srow[row & 63] = Cvt<T>::from_f(inv);
       } else {
-        st.x = 1.0f / row_sum;
+        st.x = __frcp_rn(row_sum);
       }
       // Row statistics for the epilogue group.  The 4-deep ring cannot be overrun: item n+4 of this
       // group needs P[n%2] free twice over, i.e. the second contraction of item n+2, which needs
