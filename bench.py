@@ -400,7 +400,7 @@ def run_ours(args, rank, world, local):
         "frac": achieved_tflops / peaks["bf16_tflops"],
         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the fused kernel on this workload,
         # from an `ncu --set full` capture (profiles/fused_kernel_c3_n16384_bf16.md); not measured live
-        "traffic": 194.6e6 if L_auto.kernel == _cabi.KERNEL_TCGEN05 else None,
+        "traffic": 245.8e6 if L_auto.kernel == _cabi.KERNEL_TCGEN05 else None,
         "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
         "scope": "whole op = one fused launch per step; algorithmic FLOPs / ms_per_step; `stages` = the same "
                  "kernel launched once per stage",
