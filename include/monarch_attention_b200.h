@@ -59,7 +59,8 @@ enum { MA_B200_F32 = 0, MA_B200_BF16 = 1, MA_B200_F16 = 2 };
  *   TCGEN05_STAGED the same kernel launched once per stage (for per-stage timing)
  *   TCGEN05_TILE   one-tile-per-CTA tcgen05 stage kernels (2T launches; cross-check)
  *   WARP_MMA       warp-level tensor-core stage kernels for 16-bit inputs with block size and
- *                  block count up to 128 and D <= 80 (2T launches; masks and padding handled)
+ *                  block count up to 256 and D <= 80 (D <= 64 when either exceeds 128)
+ *                  (2T launches; masks and padding handled)
  *   HEAD_FUSED     one CTA per head, one iteration (T = 1), block size and count <= 32, D <= 64:
  *                  both stages in one launch with al, y, cl in shared memory (1 launch) */
 enum {
@@ -171,6 +172,28 @@ MA_B200_API size_t ma_b200_static_scratch_bytes(void);
 MA_B200_API const char* ma_b200_static_scratch_last_error(void);
 
 /* Library ABI version (MA_B200_ABI_VERSION at build time). */
+/*
+ * Forward pass for q, k, v and the result in HOST memory, PCIe copies overlapped with the
+ * kernels.  No counterpart in the reference, whose module is handed device tensors
+ * (reference: ma/monarch_attention.py:50-59) and leaves the copies to its caller.
+ *
+ * p->q, k, v, out (and p->mask) are HOST pointers with the usual element strides; page-locked
+ * memory is needed for the copies to overlap, pageable memory works but serialises.  The
+ * (batch, head) pairs are processed in chunks of heads_per_chunk heads: H2D of chunk i+1,
+ * ma_b200_forward on chunk i and D2H of chunk i-1 run on three streams owned by the library,
+ * with three staging slots and the chunk workspace in device_scratch (256-byte aligned, at
+ * least ma_b200_host_scratch_bytes(p, heads_per_chunk) bytes; 0 = invalid problem).
+ * The call only queues work: it is ordered after what is already queued on `stream`, and on
+ * return `stream` has been made to wait for the last kernel and the last copy, so the result
+ * is in p->out once `stream` has been synchronised.  Calls on one device share the library's
+ * streams and events and must not overlap in time (one host thread, one caller stream, or
+ * explicit ordering by the caller).  Failure detail: ma_b200_host_last_error().
+ */
+MA_B200_API size_t ma_b200_host_scratch_bytes(const ma_b200_problem* p, int heads_per_chunk);
+MA_B200_API int ma_b200_forward_host(const ma_b200_problem* p, int heads_per_chunk, void* device_scratch,
+                                     size_t scratch_bytes, void* stream);
+MA_B200_API const char* ma_b200_host_last_error(void);
+
 MA_B200_API int32_t ma_b200_abi_version(void);
 
 #ifdef __cplusplus

@@ -22,6 +22,7 @@ EXPORTS = (
     "ma_b200_workspace_bytes", "ma_b200_workspace_layout_of", "ma_b200_forward", "ma_b200_forward_timed",
     "ma_b200_device_status", "ma_b200_status_string", "ma_b200_last_error", "ma_b200_abi_version",
     "ma_b200_forward_static_scratch", "ma_b200_static_scratch_bytes", "ma_b200_static_scratch_last_error",
+    "ma_b200_host_scratch_bytes", "ma_b200_forward_host", "ma_b200_host_last_error",
 )
 
 
@@ -81,19 +82,26 @@ def load() -> C.CDLL:
     lib.ma_b200_static_scratch_bytes.restype = C.c_size_t
     lib.ma_b200_static_scratch_last_error.argtypes = []
     lib.ma_b200_static_scratch_last_error.restype = C.c_char_p
+    lib.ma_b200_host_scratch_bytes.argtypes = [pp, C.c_int]
+    lib.ma_b200_host_scratch_bytes.restype = C.c_size_t
+    lib.ma_b200_forward_host.argtypes = [pp, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.ma_b200_forward_host.restype = C.c_int
+    lib.ma_b200_host_last_error.argtypes = []
+    lib.ma_b200_host_last_error.restype = C.c_char_p
     if lib.ma_b200_abi_version() != ABI_VERSION:
         raise RuntimeError("libmonarch_attention_b200.so was built for a different ABI version; rebuild it")
     _lib = lib
     return lib
 
 
-def raise_for_status(code: int) -> None:
+def raise_for_status(code: int, detail: str | None = None) -> None:
     """Map a return code to the Python exception the module API documents."""
     if code == OK:
         return
     lib = load()
     text = lib.ma_b200_status_string(code).decode()
-    detail = lib.ma_b200_last_error().decode()
+    if detail is None:
+        detail = lib.ma_b200_last_error().decode()
     msg = f"monarch_attention_b200: {text}: {detail}"
     if code in (INVALID_ARGUMENT, UNSUPPORTED, WORKSPACE_TOO_SMALL):
         raise ValueError(msg)

@@ -84,6 +84,13 @@ def _check_inputs(q: Tensor, k: Tensor, v: Tensor, attn_mask: Tensor | None):
         raise RuntimeError("monarch_attention_b200 runs on CUDA tensors only (there is no CPU path)")
     if k.device != q.device or v.device != q.device:
         raise ValueError("query, key and value must be on the same device")
+    _check_device_free_inputs(q, k, v, attn_mask)
+
+
+def _check_device_free_inputs(q: Tensor, k: Tensor, v: Tensor, attn_mask: Tensor | None):
+    """Shape and dtype rules shared by the device and the host entry points."""
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise ValueError("query, key and value must have shape (batch, heads, tokens, width)")
     if k.shape != q.shape:
         raise ValueError(f"key shape {tuple(k.shape)} differs from query shape {tuple(q.shape)}")
     if v.shape[:3] != q.shape[:3]:

@@ -156,3 +156,39 @@ def test_two_rank_sharding_over_gloo(tmp_path):
     procs = [subprocess.Popen([sys.executable, str(script), str(r)]) for r in range(2)]
     codes = [p.wait(timeout=240) for p in procs]
     assert codes == [0, 0]
+
+
+def test_host_pipeline_chunk_plan():
+    from monarch_attention_b200.host_pipeline import plan_chunks
+    assert plan_chunks(2, 5, 2) == [(0, 0, 2), (0, 2, 2), (0, 4, 1), (1, 0, 2), (1, 2, 2), (1, 4, 1)]
+    assert plan_chunks(1, 3, 8) == [(0, 0, 3)]
+    assert plan_chunks(0, 4, 2) == [] and plan_chunks(3, 0, 2) == []
+    covered = sorted((e, h) for e, h0, n in plan_chunks(3, 7, 3) for h in range(h0, h0 + n))
+    assert covered == [(e, h) for e in range(3) for h in range(7)]
+    with pytest.raises(ValueError):
+        plan_chunks(1, 4, 0)
+
+
+def test_host_entry_rejects_bad_arguments_before_touching_a_gpu():
+    import torch
+    from monarch_attention_b200 import monarch_attention_b200_host
+    q = torch.zeros(1, 2, 8, 16)
+    with pytest.raises(ValueError):
+        monarch_attention_b200_host(q, torch.zeros(1, 2, 9, 16), q, None, 1, 4, False)
+    with pytest.raises(ValueError):
+        monarch_attention_b200_host(q[0], q[0], q[0], None, 1, 4, False)
+
+
+def test_host_scratch_size_is_host_arithmetic(lib):
+    p = _problem(E=2, H=5, N=300, D=64, Dv=64, block_size=16, num_steps=2)
+    one = lib.ma_b200_host_scratch_bytes(C.byref(p), 1)
+    two = lib.ma_b200_host_scratch_bytes(C.byref(p), 2)
+    big = lib.ma_b200_host_scratch_bytes(C.byref(p), 64)       # clamped to H
+    five = lib.ma_b200_host_scratch_bytes(C.byref(p), 5)
+    assert 0 < one < two < five == big
+    # three slots of (q, k, v, result) for one head, at least
+    assert one >= 3 * 4 * 300 * 64 * 4
+    assert lib.ma_b200_host_scratch_bytes(C.byref(p), 0) == 0
+    assert b"heads_per_chunk" in lib.ma_b200_host_last_error()
+    # null host pointers are refused before any CUDA call
+    assert lib.ma_b200_forward_host(C.byref(p), 2, None, 0, None) != 0

@@ -275,3 +275,25 @@ def test_full_size_paths_agree_and_heads_permute(ma, full_inputs):
     for h in (0, 11):
         ref = monarch_attention_oracle(q[:, h:h + 1].cpu(), k[:, h:h + 1].cpu(), v[:, h:h + 1].cpu(), None, 2, 128, False)
         check_close(a[:, h:h + 1].double().cpu().numpy(), ref.double().numpy(), "bf16", f"full size head {h}")
+
+
+@pytest.mark.parametrize("name,hc", [("cfg2_vit225_bf16", 5), ("cfg4_roberta_bf16", 2), ("cfg3_n16384_bf16", 1),
+                                     ("cfg1_f32", 7)])
+def test_host_entry_point_equals_device_entry_point(ma, name, hc):
+    """Chunks of heads pipelined over three streams give the bits of one call on device tensors."""
+    case = CASES_BY_NAME[name]
+    q, k, v, mask = make_inputs(case)
+    if name == "cfg3_n16384_bf16":   # more heads than one chunk
+        q, k, v = (t.expand(1, 3, *t.shape[2:]).contiguous() for t in (q, k, v))
+    want = _run(ma, case, "b200", q, k, v, mask).cpu()
+    hq, hk, hv = (t.pin_memory() for t in (q, k, v))
+    for _ in range(2):  # second call reuses the staging slots
+        got = ma.monarch_attention_b200_host(hq, hk, hv, mask, case["T"], case["B"], case["pre_pad"],
+                                             heads_per_chunk=hc)
+        assert got.device.type == "cpu" and got.shape == want.shape
+        assert torch.equal(got.view(torch.uint8), want.view(torch.uint8))
+    out = torch.empty_like(want).pin_memory()
+    ma.monarch_attention_b200_host(hq, hk, hv, mask, case["T"], case["B"], case["pre_pad"], out=out,
+                                   heads_per_chunk=hc, wait=False)
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.uint8), want.view(torch.uint8))
