@@ -82,23 +82,35 @@ __device__ __forceinline__ float quad_sum(float v) {
 }
 
 // Copies `rows` rows of `width` 16-bit elements (width a multiple of 8) into a shared tile with row
-// pitch `pitch` elements, zero-filling rows whose source pointer is null, columns [width, wpad) and
-// rows [rows, rpad).  row_ptr(r) returns the global row or nullptr.  Threads tid of nthreads cooperate.
-// The copies are asynchronous (cp.async, 16 bytes each, zero-fill by giving a source size of 0): a
-// thread queues all of its pieces without waiting, which keeps many bytes in flight per thread;
+// pitch `pitch` elements, zero-filling rows that do not exist, columns [width, 8*CHUNKS) and rows
+// [rows, rpad).  Threads tid of nthreads cooperate.  The copies are asynchronous (cp.async, 16 bytes
+// each, zero-fill by giving a source size of 0): a thread queues all of its pieces without waiting;
 // tiles_commit_and_wait() must be called before the tile is read.
-template <typename T, typename RowFn>
-__device__ __forceinline__ void load_tile(T* tile, int pitch, int rows, int rpad, int width, int wpad, RowFn row_ptr,
-                                          int tid, int nthreads, const void* any_valid_global) {
-  const int chunks = wpad >> 3, total = rpad * chunks;
-  for (int i = tid; i < total; i += nthreads) {
-    const int r = i / chunks, c = (i - r * chunks) << 3;
-    const T* src = (r < rows && c < width) ? row_ptr(r) : nullptr;
-    const void* gsrc = src != nullptr ? static_cast<const void*>(src + c) : any_valid_global;
-    const uint32_t nbytes = src != nullptr ? 16u : 0u;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(tile + r * pitch + c)), "l"(gsrc),
-                 "r"(nbytes)
+// Every source these kernels have is an arithmetic progression of rows: row r comes from element
+// offset (n0 + r*nstep)*row_stride of `base` and exists iff r < rows and 0 <= n0 + r*nstep < n_limit
+// (token index inside the sequence; for the dense state tensors n0 = 0, nstep = 1, n_limit = rows).
+// Row, column chunk, token index and source offset are carried from one 16-byte piece to the next
+// with additions only.
+template <typename T, int CHUNKS>
+__device__ __forceinline__ void load_rows(T* tile, int pitch, int rows, int rpad, int width, const T* base, int n0,
+                                          int nstep, int n_limit, long long row_stride, int tid, int nthreads,
+                                          const void* any_valid_global) {
+  int r = tid / CHUNKS, c = tid - r * CHUNKS;
+  const int dr = nthreads / CHUNKS, dc = nthreads - dr * CHUNKS;
+  int n = n0 + r * nstep;
+  const T* src = base + (long long)n * row_stride;
+  uint32_t dst = smem_addr(tile + r * pitch);
+  const int dn = dr * nstep;
+  const long long dsrc = (long long)dn * row_stride, step1 = (long long)nstep * row_stride;
+  const uint32_t ddst = (uint32_t)(dr * pitch) * (uint32_t)sizeof(T), dst1 = (uint32_t)pitch * (uint32_t)sizeof(T);
+  while (r < rpad) {
+    const bool ok = r < rows && (c << 3) < width && (unsigned)n < (unsigned)n_limit;
+    const void* gsrc = ok ? static_cast<const void*>(src + (c << 3)) : any_valid_global;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + (uint32_t)(c << 4)), "l"(gsrc),
+                 "r"(ok ? 16u : 0u)
                  : "memory");
+    c += dc; r += dr; n += dn; src += dsrc; dst += ddst;
+    if (c >= CHUNKS) { c -= CHUNKS; ++r; n += nstep; src += step1; dst += dst1; }
   }
 }
 __device__ __forceinline__ void tiles_commit_and_wait() {
