@@ -184,8 +184,8 @@ def run_reference(args, rank, world):
     # probe the cost of one head, then size the per-step sample so the run stays within ~150 s
     probe, cores = time_oracle(1, 1, 1)
     per_head = probe[0]
-    budget = 150.0 / max(args.steps + args.warmup, 1)
-    heads = int(max(1, min(w["H"], budget / per_head)))
+    seconds_per_step = 150.0 / max(args.steps + args.warmup, 1)
+    heads = int(max(1, min(w["H"], seconds_per_step / per_head)))
     times, cores = time_oracle(heads, args.steps, args.warmup)
     total = sum(times)
     # tokens/s of the full 16-head op = E*N / (time for H heads); a sample of `heads` heads scales linearly

@@ -267,9 +267,11 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
     atomicCAS(g.status, 0, code);
   };
 
-  // Register budget per warpgroup (the launch gives every thread 128): the two softmax groups hold a
+  // Registers per warpgroup (the launch gives every thread 128): the two softmax groups hold a
   // whole accumulator row each, the epilogue group half a row, the single-thread roles little.
   // 256 x 192 + 128 x 80 + 128 x 48 = 65536 = 512 x 128, so the increase can always be granted.
+  // (What setmaxnreg redistributes is the allocation the CTA was launched with - threads x registers
+  // per thread - not the whole register file: a request beyond that pool blocks for ever.)
   if (warp >= kProducerWarp) {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
   if (warp == kProducerWarp) {

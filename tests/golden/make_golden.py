@@ -3,7 +3,7 @@
 Run in a container that has the reference checked out (it cannot travel to the
 GPU box, which is why the vectors are committed):
 
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py [--ref /path/to/reference]
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py --ref /path/to/reference
 
 For every case in cases.py the script imports the reference's
 ``monarch_attention_torch`` (reference: ma/ma_torch.py:65) through its module
@@ -57,7 +57,7 @@ def summarize(out: torch.Tensor) -> dict:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", required=True, help="checkout of the reference repository")
     ap.add_argument("--out", default=os.path.join(HERE, "golden.npz"))
     args = ap.parse_args()
     sys.dont_write_bytecode = True
