@@ -61,8 +61,9 @@ enum { MA_B200_F32 = 0, MA_B200_BF16 = 1, MA_B200_F16 = 2 };
  *   WARP_MMA       warp-level tensor-core stage kernels for 16-bit inputs with block size and
  *                  block count up to 256 and D <= 80 (D <= 64 when either exceeds 128)
  *                  (2T launches; masks and padding handled)
- *   HEAD_FUSED     one CTA per head, one iteration (T = 1), block size and count <= 32, D <= 64:
- *                  both stages in one launch with al, y, cl in shared memory (1 launch) */
+ *   HEAD_FUSED     one CTA per head, one iteration (T = 1), block size and count <= 32, D <= 64,
+ *                  the head's Q, K, V, al and y together within 227 KB of shared memory: both
+ *                  stages in one launch, HBM sees Q, K, V once and the result once (1 launch) */
 enum {
   MA_B200_KERNEL_AUTO = 0,
   MA_B200_KERNEL_GENERIC = 1,

@@ -17,7 +17,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libmonarch_attention_b200.so")
 SOURCES = ["ma_api.cu", "ma_generic.cu", "ma_tc.cu", "ma_fused.cu", "ma_warp.cu", "ma_noalloc.cu", "ma_host.cu"]
-HEADERS = ["ma_common.cuh", "ma_warp_kernels.inc", "ma_warp_wide.inc", "ma_sm100.cuh", "ma_tc_plan.cuh", os.path.join("..", "..", "include", "monarch_attention_b200.h")]
+HEADERS = ["ma_common.cuh", "ma_warp_kernels.inc", "ma_warp_wide.inc", "ma_warp_head.inc", "ma_sm100.cuh", "ma_tc_plan.cuh", os.path.join("..", "..", "include", "monarch_attention_b200.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
