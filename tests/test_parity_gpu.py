@@ -303,3 +303,18 @@ def test_host_entry_point_equals_device_entry_point(ma, name, hc):
                                    heads_per_chunk=hc, wait=False)
     torch.cuda.synchronize()
     assert torch.equal(out.view(torch.uint8), want.view(torch.uint8))
+
+
+def test_host_entry_point_with_token_major_host_tensors(ma):
+    """q, k, v and the result as (E, H, N, D) views of (E, N, H, D) host buffers: pitched copies per head."""
+    case = CASES_BY_NAME["cfg2_vit225_bf16"]
+    q, k, v, mask = make_inputs(case)
+    want = _run(ma, case, "b200", q, k, v, mask).cpu()
+    tm = lambda t: t.permute(0, 2, 1, 3).contiguous().pin_memory().permute(0, 2, 1, 3)  # noqa: E731
+    hq, hk, hv = tm(q), tm(k), tm(v)
+    assert hq.stride(2) != hq.shape[3]
+    out = tm(torch.zeros_like(want))
+    got = ma.monarch_attention_b200_host(hq, hk, hv, mask, case["T"], case["B"], case["pre_pad"], out=out,
+                                         heads_per_chunk=5)
+    assert got is out
+    assert torch.equal(out.contiguous().view(torch.uint8), want.view(torch.uint8))
