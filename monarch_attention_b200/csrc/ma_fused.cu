@@ -487,7 +487,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         } else if (it.kind == kStageLeft) {
           float o[32];
           tmem_ld32(tmem_o + kHead, o);
-          g.cr[((long long)it.eh * g.M + row) * g.B + it.tile] = o[0];
+          g.cr[((long long)it.eh * g.M + row) * g.B + it.tile] = o[0] + o[1];
         }
       }
       tc_fence_before();
@@ -670,8 +670,14 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           st_shared_v4(sA + swz(row, ch), pack2<T>(a.x * inv, a.y * inv), pack2<T>(b.x * inv, b.y * inv),
                        pack2<T>(c2.x * inv, c2.y * inv), pack2<T>(d.x * inv, d.y * inv));
         }
-        T* srow = reinterpret_cast<T*>(base_ptr + kOffSv + sb * 4096 + (row >> 6) * 2048);
-        srow[row & 63] = Cvt<T>::from_f(inv);
+        // 1/rowsum as a 16-bit value plus its 16-bit remainder, in rows 0 and 1 of the 16 x 128 operand
+        // (row r, column c of a swizzled 64-column atom: r*128 + ((c/8) ^ r)*16 + (c%8)*2 bytes): the
+        // column sums cr = sum_l P[l, m] / rowsum_l then carry the rounding of P only.
+        uint8_t* atom = base_ptr + kOffSv + sb * 4096 + (row >> 6) * 2048;
+        const int c = row & 63;
+        const T hi = Cvt<T>::from_f(inv);
+        reinterpret_cast<T*>(atom)[c] = hi;
+        *reinterpret_cast<T*>(atom + 128 + (((c >> 3) ^ 1) << 4) + ((c & 7) << 1)) = Cvt<T>::from_f(inv - Cvt<T>::to_f(hi));
       } else {
         st.x = __frcp_rn(row_sum);
       }
