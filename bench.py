@@ -461,6 +461,40 @@ def run_ours(args, rank, world, local):
     print(json.dumps(line), flush=True)
 
 
+def run_layer(args):
+    """`--layer E,H,N,D,B,T,pad[,mask]`: kernel-only timing of one attention layer of another configuration
+    (ViT: 64,12,197,64,15,1,pre   RoBERTa: 32,12,512,64,32,1,post,mask   DiT: 64,16,1024,72,32,2,post
+    N = 65536: 1,16,65536,64,256,2,post), per stage, from CUDA events recorded inside the library.  Not the
+    headline line: it exists so that the other kernel families can be timed and profiled with a committed command."""
+    import ctypes as C
+
+    from monarch_attention_b200 import _cabi
+    from monarch_attention_b200.monarch_attention import make_problem
+    f = args.layer.split(",")
+    E, H, N, D, B, T = (int(x) for x in f[:6])
+    pre = len(f) > 6 and f[6] == "pre"
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn(E, H, N, D, generator=g).to(torch.bfloat16).to(dev) for _ in range(3))
+    mask = (torch.rand(E, N, generator=g) > 0.1).to(torch.uint8).to(dev) if len(f) > 7 and f[7] == "mask" else None
+    out = torch.empty_like(v)
+    lib = _cabi.load()
+    prob = make_problem(q, k, v, out, mask, T, B, pre, _cabi.KERNEL_AUTO)
+    L = _cabi.WorkspaceLayout()
+    _cabi.raise_for_status(lib.ma_b200_workspace_layout_of(C.byref(prob), C.byref(L)))
+    ws = torch.empty(L.total, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    buf = (C.c_float * (2 * T))()
+    acc = [0.0] * (2 * T)
+    for it in range(args.warmup + args.steps):
+        _cabi.raise_for_status(lib.ma_b200_forward_timed(C.byref(prob), ws.data_ptr(), ws.numel(), stream, buf, 2 * T))
+        if it >= args.warmup:
+            acc = [a + b / args.steps for a, b in zip(acc, buf)]
+    print(json.dumps({"layer": args.layer, "kernel": _cabi.KERNEL_NAMES[L.kernel], "stage_ms": acc,
+                      "ms_per_layer": sum(acc), "steps": args.steps, "warmup": args.warmup}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -468,7 +502,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layer", default=None, help="E,H,N,D,B,T,pre|post[,mask]: time one layer of that shape instead")
     args = ap.parse_args()
+    if args.layer:
+        run_layer(args)
+        return
     if args.impl == "reference":
         rank = int(os.environ.get("RANK", "0"))
         run_reference(args, rank, int(os.environ.get("WORLD_SIZE", "1")))
