@@ -339,7 +339,8 @@ def run_ours(args, rank, world, local):
     def e2e_step():
         # the package's host-buffer entry point: chunks of heads, H2D / kernels / D2H on three streams;
         # steps do not overlap one another (the caller's stream waits for the last D2H of every step)
-        monarch_attention_b200_host(hq, hk, hv, None, w["T"], w["B"], False, out=hout, wait=False)
+        monarch_attention_b200_host(hq, hk, hv, None, w["T"], w["B"], False, out=hout, wait=False,
+                                    heads_per_chunk=args.e2e_heads_per_chunk)
 
     for _ in range(3):
         e2e_step()
@@ -452,7 +453,8 @@ def run_ours(args, rank, world, local):
         "clocks": sampler.summary(),
         "e2e": {"value": tokens_per_step / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps,
-                "api": "monarch_attention_b200_host: pinned host q, k, v in, pinned host result out, 4 heads per chunk"},
+                "api": "monarch_attention_b200_host: pinned host q, k, v in, pinned host result out, "
+                       f"{args.e2e_heads_per_chunk} heads per chunk"},
         "gpu_launches": args.steps * (1 if L_auto.kernel == _cabi.KERNEL_TCGEN05 else n_stage),
         "roofline": roofline,
         "cpu_baseline": cpu_baseline,
@@ -502,6 +504,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-heads-per-chunk", type=int, default=4,
+                    help="heads per pipeline chunk of the end-to-end (host memory) measurement")
     ap.add_argument("--layer", default=None, help="E,H,N,D,B,T,pre|post[,mask]: time one layer of that shape instead")
     args = ap.parse_args()
     if args.layer:
