@@ -504,7 +504,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--e2e-heads-per-chunk", type=int, default=4,
+    ap.add_argument("--e2e-heads-per-chunk", type=int, default=8,
                     help="heads per pipeline chunk of the end-to-end (host memory) measurement")
     ap.add_argument("--layer", default=None, help="E,H,N,D,B,T,pre|post[,mask]: time one layer of that shape instead")
     args = ap.parse_args()

@@ -180,7 +180,8 @@ MA_B200_API const char* ma_b200_static_scratch_last_error(void);
  *
  * p->q, k, v, out (and p->mask) are HOST pointers with the usual element strides; page-locked
  * memory is needed for the copies to overlap, pageable memory works but serialises.  The
- * (batch, head) pairs are processed in chunks of heads_per_chunk heads: H2D of chunk i+1,
+ * (batch, head) pairs are processed in chunks of heads_per_chunk heads (smaller ones at the very
+ * end, so that little work is left once the last copy-in has landed): H2D of chunk i+1,
  * ma_b200_forward on chunk i and D2H of chunk i-1 run on three streams owned by the library,
  * with three staging slots and the chunk workspace in device_scratch (256-byte aligned, at
  * least ma_b200_host_scratch_bytes(p, heads_per_chunk) bytes; 0 = invalid problem).

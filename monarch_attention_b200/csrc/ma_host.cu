@@ -8,7 +8,8 @@
 //     compute : ma_b200_forward on chunk i (device staging buffers, E = 1, H = heads of the chunk)
 //     copy-out: D2H result of chunk i-1
 // - with three staging slots in caller-provided device memory and events between the streams.
-// PCIe is full duplex, so the steady state is bound by the larger copy direction alone.
+// PCIe is full duplex, so the steady state is bound by the larger copy direction alone; the chunks of
+// the last batch element shrink towards the end so that little is left exposed after the last copy-in.
 // The whole pipeline is queued from one host thread without waiting for the GPU; on return the
 // caller's stream has been made to wait for the last copy.
 #include <mutex>
@@ -186,8 +187,14 @@ MA_B200_API int ma_b200_forward_host(const ma_b200_problem* p, int heads_per_chu
 
   int i = 0;
   for (int e = 0; e < p->E; ++e) {
-    for (int h0 = 0; h0 < p->H; h0 += L.hc, ++i) {
-      const int nh = p->H - h0 < L.hc ? p->H - h0 : L.hc;
+    int nh = 0;
+    for (int h0 = 0; h0 < p->H; h0 += nh, ++i) {
+      // Chunks of hc heads, except that the last batch element tapers off (each chunk at most half of
+      // what is left): once the last copy-in has landed, only the kernels and the copy-out of the last
+      // chunk are still to come, and nothing overlaps them.
+      const int left = p->H - h0;
+      nh = left < L.hc ? left : L.hc;
+      if (e == p->E - 1 && nh > 1 && nh > left / 2) nh = left / 2 > 1 ? left / 2 : 1;
       const int slot = i % kSlots;
       char* sq = base + (size_t)slot * L.slot_bytes;
       char* sk = sq + L.qk_bytes;

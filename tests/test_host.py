@@ -160,8 +160,10 @@ def test_two_rank_sharding_over_gloo(tmp_path):
 
 def test_host_pipeline_chunk_plan():
     from monarch_attention_b200.host_pipeline import plan_chunks
-    assert plan_chunks(2, 5, 2) == [(0, 0, 2), (0, 2, 2), (0, 4, 1), (1, 0, 2), (1, 2, 2), (1, 4, 1)]
-    assert plan_chunks(1, 3, 8) == [(0, 0, 3)]
+    # full chunks, except that the last batch element tapers off (each chunk at most half of what is left)
+    assert plan_chunks(2, 5, 2) == [(0, 0, 2), (0, 2, 2), (0, 4, 1), (1, 0, 2), (1, 2, 1), (1, 3, 1), (1, 4, 1)]
+    assert plan_chunks(1, 3, 8) == [(0, 0, 1), (0, 1, 1), (0, 2, 1)]
+    assert [n for _, _, n in plan_chunks(1, 16, 4)] == [4, 4, 4, 2, 1, 1]
     assert plan_chunks(0, 4, 2) == [] and plan_chunks(3, 0, 2) == []
     covered = sorted((e, h) for e, h0, n in plan_chunks(3, 7, 3) for h in range(h0, h0 + n))
     assert covered == [(e, h) for e in range(3) for h in range(7)]
