@@ -10,8 +10,9 @@
 // Work decomposition: one CTA per (head, key block m) for the right-factor stages and
 // per (head, column j) for the left-factor and output stages; one warp per row of the
 // small attention problem; lanes run over keys for the logits and over the feature
-// axis for the weighted sums.  Operand rows are read straight from global memory
-// (they are L1/L2 resident for the tile a CTA works on).
+// axis for the weighted sums.  The operand tiles of a CTA are converted to fp32 and kept in shared
+// memory when they fit (see "Operand tiles in shared memory" below); otherwise their rows are read
+// straight from global memory.
 #include <math.h>
 
 #include "ma_common.cuh"
@@ -42,12 +43,46 @@ __device__ __forceinline__ float dot_row(const float* __restrict__ a, const T* _
   return acc;
 }
 
+// The same dot product with the row already converted to fp32 in shared memory.
+__device__ __forceinline__ float dot_smem(const float* __restrict__ a, const float* __restrict__ row, int D) {
+  float acc = 0.f;
+  for (int d = 0; d < D; ++d) acc = fmaf(a[d], row[d], acc);
+  return acc;
+}
+
 // Token row of a (E,H,N,W) view for padded position p, or nullptr when p is padding.
 template <typename T>
 __device__ __forceinline__ const T* token_row(const View4& t, int e, int h, int p, int pad_off, int N) {
   int n = p - pad_off;
   if (n < 0 || n >= N) return nullptr;
   return reinterpret_cast<const T*>(t.ptr) + (long long)e * t.se + (long long)h * t.sh + (long long)n * t.sn;
+}
+
+// Operand tiles in shared memory.  When they fit, the rows a CTA works on are converted to fp32 once and
+// kept in shared memory with a row pitch of W + 1 floats (lanes that walk down a column of rows then hit
+// 32 different banks); rows that do not exist (padding) are zero, which gives the same sums as skipping
+// them.  Every product and every sum is formed in the same order as on the path that reads the rows from
+// global memory, so the two paths return the same bits; the staged one just does not issue one
+// uncoalesced global load per multiply.
+enum { kStageKeys = 1, kStageValues = 2, kStageQueries = 4 };
+
+// rows `r` = 0..rows-1 of a user tensor at padded positions p0 + r * pstep
+template <typename T>
+__device__ __forceinline__ void stage_token_rows(float* dst, const View4& t, int e, int h, int p0, int pstep, int rows,
+                                                 int W, const Geometry& g) {
+  for (int idx = threadIdx.x; idx < rows * W; idx += blockDim.x) {
+    const int r = idx / W, d = idx - r * W;
+    const T* row = token_row<T>(t, e, h, p0 + r * pstep, g.pad_off, g.N);
+    dst[r * (W + 1) + d] = row ? Cvt<T>::to_f(row[d]) : 0.f;
+  }
+}
+// rows of a dense (rows, W) state tensor
+template <typename T>
+__device__ __forceinline__ void stage_dense_rows(float* dst, const T* src, int rows, int W) {
+  for (int idx = threadIdx.x; idx < rows * W; idx += blockDim.x) {
+    const int r = idx / W, d = idx - r * W;
+    dst[r * (W + 1) + d] = Cvt<T>::to_f(src[idx]);
+  }
 }
 
 __device__ __forceinline__ bool token_valid(const Geometry& g, int e, int p) {
@@ -61,7 +96,7 @@ __device__ __forceinline__ bool token_valid(const Geometry& g, int e, int p) {
 // grid = (M, E*H).  Shared memory: kWarps*(D + B) floats.
 // ---------------------------------------------------------------------------------
 template <typename TQ, typename TV, bool WITH_V>
-__global__ void __launch_bounds__(kThreads) right_stage_kernel(const Geometry g, const int first) {
+__global__ void __launch_bounds__(kThreads) right_stage_kernel(const Geometry g, const int first, const int staged) {
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m = blockIdx.x, eh = blockIdx.y;
@@ -69,6 +104,16 @@ __global__ void __launch_bounds__(kThreads) right_stage_kernel(const Geometry g,
   const int B = g.B, D = g.D, Dv = g.Dv, M = g.M;
   float* avec = smem + warp * (D + B);
   float* rbuf = avec + D;
+  float* sK = nullptr;
+  float* sV = nullptr;
+  {
+    float* next = smem + kWarps * (D + B);
+    if (staged & kStageKeys) { sK = next; next += (size_t)B * (D + 1); }
+    if (WITH_V && (staged & kStageValues)) sV = next;
+    if (sK) stage_token_rows<TQ>(sK, g.k, e, h, m * B, 1, B, D, g);
+    if (sV) stage_token_rows<TV>(sV, g.v, e, h, m * B, 1, B, Dv, g);
+    if (sK || sV) __syncthreads();
+  }
 
   const TQ* ar = reinterpret_cast<const TQ*>(g.ar) + ((long long)eh * M + m) * B * D;
   TQ* al = reinterpret_cast<TQ*>(g.al) + (long long)eh * B * M * D;
@@ -91,8 +136,13 @@ __global__ void __launch_bounds__(kThreads) right_stage_kernel(const Geometry g,
 
     float vmax = -INFINITY;
     for (int i = lane; i < B; i += 32) {
-      const TQ* krow = token_row<TQ>(g.k, e, h, m * B + i, g.pad_off, g.N);
-      float dot = krow ? dot_row<TQ>(avec, krow, D) : 0.f;
+      float dot;
+      if (sK) {
+        dot = dot_smem(avec, sK + (size_t)i * (D + 1), D);
+      } else {
+        const TQ* krow = token_row<TQ>(g.k, e, h, m * B + i, g.pad_off, g.N);
+        dot = krow ? dot_row<TQ>(avec, krow, D) : 0.f;
+      }
       float x = (g.sm_scale * round_through<TQ>(dot)) / denom_c;
       if (!token_valid(g, e, m * B + i)) x = -INFINITY;
       rbuf[i] = x;
@@ -118,9 +168,13 @@ __global__ void __launch_bounds__(kThreads) right_stage_kernel(const Geometry g,
 
     for (int d = lane; d < D; d += 32) {
       float acc = 0.f;
-      for (int i = 0; i < B; ++i) {
-        const TQ* krow = token_row<TQ>(g.k, e, h, m * B + i, g.pad_off, g.N);
-        if (krow) acc = fmaf(round_through<TQ>(rbuf[i]), Cvt<TQ>::to_f(krow[d]), acc);
+      if (sK) {
+        for (int i = 0; i < B; ++i) acc = fmaf(round_through<TQ>(rbuf[i]), sK[(size_t)i * (D + 1) + d], acc);
+      } else {
+        for (int i = 0; i < B; ++i) {
+          const TQ* krow = token_row<TQ>(g.k, e, h, m * B + i, g.pad_off, g.N);
+          if (krow) acc = fmaf(round_through<TQ>(rbuf[i]), Cvt<TQ>::to_f(krow[d]), acc);
+        }
       }
       // sm_scale * (r @ k): the product is rounded to storage, scaled, rounded again (:21)
       al[((long long)j * M + m) * D + d] = Cvt<TQ>::from_f(g.sm_scale * round_through<TQ>(acc));
@@ -128,9 +182,13 @@ __global__ void __launch_bounds__(kThreads) right_stage_kernel(const Geometry g,
     if (WITH_V) {
       for (int d = lane; d < Dv; d += 32) {
         float acc = 0.f;
-        for (int i = 0; i < B; ++i) {
-          const TV* vrow = token_row<TV>(g.v, e, h, m * B + i, g.pad_off, g.N);
-          if (vrow) acc = fmaf(round_through<TV>(rbuf[i]), Cvt<TV>::to_f(vrow[d]), acc);
+        if (sV) {
+          for (int i = 0; i < B; ++i) acc = fmaf(round_through<TV>(rbuf[i]), sV[(size_t)i * (Dv + 1) + d], acc);
+        } else {
+          for (int i = 0; i < B; ++i) {
+            const TV* vrow = token_row<TV>(g.v, e, h, m * B + i, g.pad_off, g.N);
+            if (vrow) acc = fmaf(round_through<TV>(rbuf[i]), Cvt<TV>::to_f(vrow[d]), acc);
+          }
         }
         y[((long long)j * M + m) * Dv + d] = Cvt<TV>::from_f(acc);
       }
@@ -147,7 +205,7 @@ __global__ void __launch_bounds__(kThreads) right_stage_kernel(const Geometry g,
 // Shared memory: kWarps*(D + M) + 3*M floats.
 // ---------------------------------------------------------------------------------
 template <typename TQ>
-__global__ void __launch_bounds__(kThreads) left_stage_kernel(const Geometry g) {
+__global__ void __launch_bounds__(kThreads) left_stage_kernel(const Geometry g, const int staged) {
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int j = blockIdx.x, eh = blockIdx.y;
@@ -163,6 +221,16 @@ __global__ void __launch_bounds__(kThreads) left_stage_kernel(const Geometry g) 
   const float* cl = g.cl + ((long long)eh * B + j) * M;
   TQ* ar = reinterpret_cast<TQ*>(g.ar) + (long long)eh * M * B * D;
   float* cr = g.cr + (long long)eh * M * B;
+  float* sAL = nullptr;  // al[j]: (M, D)
+  float* sQ = nullptr;   // q column j: rows l = 0..M-1
+  {
+    float* next = s_ok + M;
+    if (staged & kStageKeys) { sAL = next; next += (size_t)M * (D + 1); }
+    if (staged & kStageQueries) sQ = next;
+    if (sAL) stage_dense_rows<TQ>(sAL, al, M, D);
+    if (sQ) stage_token_rows<TQ>(sQ, g.q, e, h, j, B, M, D, g);
+    if (sAL || sQ) __syncthreads();
+  }
 
   for (int l = warp; l < M; l += kWarps) {
     const TQ* qrow = token_row<TQ>(g.q, e, h, l * B + j, g.pad_off, g.N);
@@ -170,7 +238,8 @@ __global__ void __launch_bounds__(kThreads) left_stage_kernel(const Geometry g) 
     __syncwarp();
     float vmax = -INFINITY;
     for (int mm = lane; mm < M; mm += 32) {
-      float w = round_through<TQ>(dot_row<TQ>(avec, al + (long long)mm * D, D)) - cl[mm];
+      const float dot = sAL ? dot_smem(avec, sAL + (size_t)mm * (D + 1), D) : dot_row<TQ>(avec, al + (long long)mm * D, D);
+      float w = round_through<TQ>(dot) - cl[mm];
       rbuf[mm] = w;
       vmax = fmaxf(vmax, w);
     }
@@ -188,16 +257,20 @@ __global__ void __launch_bounds__(kThreads) left_stage_kernel(const Geometry g) 
   __syncthreads();
 
   for (int mm = warp; mm < M; mm += kWarps) {
-    for (int d = lane; d < D; d += 32) avec[d] = Cvt<TQ>::to_f(al[(long long)mm * D + d]);
+    for (int d = lane; d < D; d += 32) avec[d] = sAL ? sAL[(size_t)mm * (D + 1) + d] : Cvt<TQ>::to_f(al[(long long)mm * D + d]);
     __syncwarp();
     const float c = cl[mm];
     float colsum = 0.f;
     for (int l = lane; l < M; l += 32) {
-      const TQ* qrow = token_row<TQ>(g.q, e, h, l * B + j, g.pad_off, g.N);
       float dot = 0.f;
-      if (qrow) {
-        // same products in the same order as pass 1 (fmaf(a, b, acc) with a, b swapped is identical)
-        for (int d = 0; d < D; ++d) dot = fmaf(Cvt<TQ>::to_f(qrow[d]), avec[d], dot);
+      // same products in the same order as pass 1 (fmaf(a, b, acc) with a, b swapped is identical)
+      if (sQ) {
+        const float* qs = sQ + (size_t)l * (D + 1);
+        for (int d = 0; d < D; ++d) dot = fmaf(qs[d], avec[d], dot);
+      } else {
+        const TQ* qrow = token_row<TQ>(g.q, e, h, l * B + j, g.pad_off, g.N);
+        if (qrow)
+          for (int d = 0; d < D; ++d) dot = fmaf(Cvt<TQ>::to_f(qrow[d]), avec[d], dot);
       }
       float w = round_through<TQ>(dot) - c;
       float p = s_ok[l] * (expf(w - s_max[l]) / s_sum[l]);
@@ -209,9 +282,13 @@ __global__ void __launch_bounds__(kThreads) left_stage_kernel(const Geometry g) 
     __syncwarp();
     for (int d = lane; d < D; d += 32) {
       float acc = 0.f;
-      for (int l = 0; l < M; ++l) {
-        const TQ* qrow = token_row<TQ>(g.q, e, h, l * B + j, g.pad_off, g.N);
-        if (qrow) acc = fmaf(round_through<TQ>(rbuf[l]), Cvt<TQ>::to_f(qrow[d]), acc);
+      if (sQ) {
+        for (int l = 0; l < M; ++l) acc = fmaf(round_through<TQ>(rbuf[l]), sQ[(size_t)l * (D + 1) + d], acc);
+      } else {
+        for (int l = 0; l < M; ++l) {
+          const TQ* qrow = token_row<TQ>(g.q, e, h, l * B + j, g.pad_off, g.N);
+          if (qrow) acc = fmaf(round_through<TQ>(rbuf[l]), Cvt<TQ>::to_f(qrow[d]), acc);
+        }
       }
       ar[((long long)mm * B + j) * D + d] = Cvt<TQ>::from_f(acc);
     }
@@ -224,7 +301,7 @@ __global__ void __launch_bounds__(kThreads) left_stage_kernel(const Geometry g) 
 // every real token gets an output row.  Shared memory: kWarps*(D + M) floats.
 // ---------------------------------------------------------------------------------
 template <typename TQ, typename TV>
-__global__ void __launch_bounds__(kThreads) output_stage_kernel(const Geometry g) {
+__global__ void __launch_bounds__(kThreads) output_stage_kernel(const Geometry g, const int staged) {
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int j = blockIdx.x, eh = blockIdx.y;
@@ -236,6 +313,16 @@ __global__ void __launch_bounds__(kThreads) output_stage_kernel(const Geometry g
   const TQ* al = reinterpret_cast<const TQ*>(g.al) + ((long long)eh * B + j) * M * D;
   const float* cl = g.cl + ((long long)eh * B + j) * M;
   const TV* y = reinterpret_cast<const TV*>(g.y) + ((long long)eh * B + j) * M * Dv;
+  float* sAL = nullptr;  // al[j]: (M, D)
+  float* sY = nullptr;   // y[j]: (M, Dv)
+  {
+    float* next = smem + kWarps * (D + M);
+    if (staged & kStageKeys) { sAL = next; next += (size_t)M * (D + 1); }
+    if (staged & kStageValues) sY = next;
+    if (sAL) stage_dense_rows<TQ>(sAL, al, M, D);
+    if (sY) stage_dense_rows<TV>(sY, y, M, Dv);
+    if (sAL || sY) __syncthreads();
+  }
 
   for (int l = warp; l < M; l += kWarps) {
     const int n = l * B + j - g.pad_off;
@@ -245,7 +332,8 @@ __global__ void __launch_bounds__(kThreads) output_stage_kernel(const Geometry g
     __syncwarp();
     float vmax = -INFINITY;
     for (int mm = lane; mm < M; mm += 32) {
-      float w = round_through<TQ>(dot_row<TQ>(avec, al + (long long)mm * D, D)) - cl[mm];
+      const float dot = sAL ? dot_smem(avec, sAL + (size_t)mm * (D + 1), D) : dot_row<TQ>(avec, al + (long long)mm * D, D);
+      float w = round_through<TQ>(dot) - cl[mm];
       rbuf[mm] = w;
       vmax = fmaxf(vmax, w);
     }
@@ -262,17 +350,43 @@ __global__ void __launch_bounds__(kThreads) output_stage_kernel(const Geometry g
                (long long)h * g.out.sh + (long long)n * g.out.sn;
     for (int d = lane; d < Dv; d += 32) {
       float acc = 0.f;
-      for (int mm = 0; mm < M; ++mm)
-        acc = fmaf(round_through<TV>(rbuf[mm] / vsum), Cvt<TV>::to_f(y[(long long)mm * Dv + d]), acc);
+      if (sY) {
+        for (int mm = 0; mm < M; ++mm) acc = fmaf(round_through<TV>(rbuf[mm] / vsum), sY[(size_t)mm * (Dv + 1) + d], acc);
+      } else {
+        for (int mm = 0; mm < M; ++mm)
+          acc = fmaf(round_through<TV>(rbuf[mm] / vsum), Cvt<TV>::to_f(y[(long long)mm * Dv + d]), acc);
+      }
       orow[d] = Cvt<TV>::from_f(acc);
     }
     __syncwarp();
   }
 }
 
+// Which operand tiles go to shared memory (kStage* bits) and the bytes that takes on top of `base`.
+// Tiles are added while the total stays within 160 KB; a tile that does not fit is read from global
+// memory as before (the explicit-matrix case, whose value rows are N wide, is the usual one).
+int staging_plan(const Geometry& g, StageKind kind, size_t base, size_t* total) {
+  const size_t limit = 160 * 1024;
+  int flags = 0;
+  size_t bytes = base;
+  auto add = [&](int bit, size_t rows, size_t width) {
+    const size_t need = rows * (width + 1) * sizeof(float);
+    if (bytes + need <= limit) { flags |= bit; bytes += need; }
+  };
+  switch (kind) {
+    case kStageRight: add(kStageKeys, g.B, g.D); break;
+    case kStageRightWithV: add(kStageKeys, g.B, g.D); add(kStageValues, g.B, g.Dv); break;
+    case kStageLeft: add(kStageKeys, g.M, g.D); add(kStageQueries, g.M, g.D); break;
+    case kStageOutput: add(kStageKeys, g.M, g.D); add(kStageValues, g.M, g.Dv); break;
+  }
+  *total = bytes;
+  return flags;
+}
+
 template <typename TQ, typename TV>
 cudaError_t launch_typed(const Geometry& g, StageKind kind, bool first, cudaStream_t stream) {
-  const size_t smem = generic_stage_smem_bytes(g, kind);
+  size_t smem = 0;
+  const int staged = staging_plan(g, kind, generic_stage_smem_bytes(g, kind), &smem);
   const dim3 block(kThreads);
   const int EH = g.E * g.H;
   auto raise = [&](const void* fn) -> cudaError_t {
@@ -283,19 +397,19 @@ cudaError_t launch_typed(const Geometry& g, StageKind kind, bool first, cudaStre
   switch (kind) {
     case kStageRight:
       if ((err = raise((const void*)right_stage_kernel<TQ, TV, false>)) != cudaSuccess) return err;
-      right_stage_kernel<TQ, TV, false><<<dim3(g.M, EH), block, smem, stream>>>(g, first ? 1 : 0);
+      right_stage_kernel<TQ, TV, false><<<dim3(g.M, EH), block, smem, stream>>>(g, first ? 1 : 0, staged);
       break;
     case kStageRightWithV:
       if ((err = raise((const void*)right_stage_kernel<TQ, TV, true>)) != cudaSuccess) return err;
-      right_stage_kernel<TQ, TV, true><<<dim3(g.M, EH), block, smem, stream>>>(g, first ? 1 : 0);
+      right_stage_kernel<TQ, TV, true><<<dim3(g.M, EH), block, smem, stream>>>(g, first ? 1 : 0, staged);
       break;
     case kStageLeft:
       if ((err = raise((const void*)left_stage_kernel<TQ>)) != cudaSuccess) return err;
-      left_stage_kernel<TQ><<<dim3(g.B, EH), block, smem, stream>>>(g);
+      left_stage_kernel<TQ><<<dim3(g.B, EH), block, smem, stream>>>(g, staged);
       break;
     case kStageOutput:
       if ((err = raise((const void*)output_stage_kernel<TQ, TV>)) != cudaSuccess) return err;
-      output_stage_kernel<TQ, TV><<<dim3(g.B, EH), block, smem, stream>>>(g);
+      output_stage_kernel<TQ, TV><<<dim3(g.B, EH), block, smem, stream>>>(g, staged);
       break;
   }
   return cudaGetLastError();
