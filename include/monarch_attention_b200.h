@@ -55,9 +55,11 @@ enum { MA_B200_F32 = 0, MA_B200_BF16 = 1, MA_B200_F16 = 2 };
 /* Kernel families.  AUTO picks the fused tcgen05 kernel when the problem fits it, else the
  * warp-level tensor-core kernels, else the generic kernels.
  *   GENERIC        SIMT stage kernels, any shape / dtype / mask (2T launches)
- *   TCGEN05        persistent tcgen05 kernel, all 2T stages in one launch
+ *   TCGEN05        persistent tcgen05 kernel, all 2T stages in one launch: 16-bit inputs,
+ *                  D = Dv = 64, no mask, no padding, block size = block count = 128 or 64
  *   TCGEN05_STAGED the same kernel launched once per stage (for per-stage timing)
- *   TCGEN05_TILE   one-tile-per-CTA tcgen05 stage kernels (2T launches; cross-check)
+ *   TCGEN05_TILE   one-tile-per-CTA tcgen05 stage kernels, block size 128 only
+ *                  (2T launches; cross-check)
  *   WARP_MMA       warp-level tensor-core stage kernels for 16-bit inputs with block size and
  *                  block count up to 256 and D <= 80 (D <= 64 when either exceeds 128)
  *                  (2T launches; masks and padding handled)

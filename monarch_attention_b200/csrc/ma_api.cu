@@ -89,6 +89,8 @@ int resolve_kernel(const ma_b200_problem* p, const ma::Geometry& g, int* kernel)
   const bool wants_tc = p->kernel >= MA_B200_KERNEL_TCGEN05 && p->kernel <= MA_B200_KERNEL_TCGEN05_TILE;
   if (wants_tc && !tc_ok)
     return fail(MA_B200_UNSUPPORTED, std::string("tcgen05 path cannot run this problem: ") + why);
+  if (p->kernel == MA_B200_KERNEL_TCGEN05_TILE && g.B != 128)
+    return fail(MA_B200_UNSUPPORTED, "one-tile-per-CTA tcgen05 kernels need block size = block count = 128");
   const char* why_w = "";
   const bool warp_ok = ma::warp_supported(g, p->qk_dtype, p->v_dtype, &why_w);
   if (p->kernel == MA_B200_KERNEL_WARP_MMA && !warp_ok)

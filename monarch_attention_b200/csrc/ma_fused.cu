@@ -112,6 +112,7 @@ struct Item {
 struct ItemCursor {
   int gi, sl, hh, tile, gh;  // group, stage within the launch, head within the group, tile, heads in this group
   int idx, total, stride, nst, group, EH, stage_begin, last_stage;
+  int tph;       // tiles per head and stage: N / 128
   int ring_pos;  // next free tile of the operand ring (advanced by take())
 
   __device__ __forceinline__ void init(int first_idx, int stride_, const Geometry& g, const FusedArgs& a) {
@@ -120,30 +121,31 @@ struct ItemCursor {
     group = a.group;
     stage_begin = a.stage_begin;
     last_stage = 2 * g.T - 1;
+    tph = g.N / kTile;
 #ifdef MA_DIAG
-    total = (a.dbg & 32) ? 0 : nst * kTile * EH;
+    total = (a.dbg & 32) ? 0 : nst * tph * EH;
 #else
-    total = nst * kTile * EH;
+    total = nst * tph * EH;
 #endif
     stride = stride_;
     idx = first_idx;
     ring_pos = 0;
-    const int per_group = nst * group * kTile;
+    const int per_group = nst * group * tph;
     gi = idx / per_group;
     int r = idx - gi * per_group;
     gh = min(group, EH - gi * group);
     if (gh < 1) gh = 1;
-    sl = r / (gh * kTile);
-    r -= sl * gh * kTile;
-    hh = r / kTile;
-    tile = r - hh * kTile;
+    sl = r / (gh * tph);
+    r -= sl * gh * tph;
+    hh = r / tph;
+    tile = r - hh * tph;
   }
   __device__ __forceinline__ bool valid() const { return idx < total; }
   __device__ __forceinline__ void next() {
     idx += stride;
     tile += stride;
-    while (tile >= kTile) {
-      tile -= kTile;
+    while (tile >= tph) {
+      tile -= tph;
       if (++hh == gh) {
         hh = 0;
         if (++sl == nst) {
@@ -185,7 +187,7 @@ struct ItemCursor {
   }
 };
 
-template <typename T>
+template <typename T, int PER>  // PER: key blocks (or columns j) per 128-row tile: 1 (block size 128) or 2 (64)
 __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constant__ TcMaps maps, const Geometry g,
                                                             const FusedArgs args) {
   extern __shared__ uint8_t smem_raw[];
@@ -203,7 +205,10 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
   constexpr int dbg_flags = 0;
 #endif
   constexpr int kFmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
-  const int total = (dbg_flags & 32) ? 0 : (args.stage_end - args.stage_begin) * kTile * g.E * g.H;
+  const int tph = g.N / kTile;        // tiles per head and stage
+  constexpr int per = PER;
+  constexpr int kRowsPer = kTile / PER;  // rows of one block (or column) inside a tile = block size = block count
+  const int total = (dbg_flags & 32) ? 0 : (args.stage_end - args.stage_begin) * tph * g.E * g.H;
   const int nst_all = 2 * g.T;
 
 
@@ -240,6 +245,12 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
   {  // zero both 16 x 128 operands that will carry 1/rowsum in their first row (left-factor stage)
     uint32_t* z = reinterpret_cast<uint32_t*>(base_ptr + kOffSv);
     for (int i = tid; i < 2 * 1024; i += kThreads) z[i] = 0u;
+    // With two blocks per tile every row of P has entries only in the 64 columns of its own block; the
+    // other 64 are never written and have to read as zero in the second contraction.
+    if (per > 1) {
+      uint4* zp = reinterpret_cast<uint4*>(base_ptr + kOffP);
+      for (int i = tid; i < (int)(2 * 2 * kTileBytes / 16); i += kThreads) zp[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
   }
   fence_async_smem();
   tc_fence_before();
@@ -291,7 +302,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           const int* ctr = args.counters + it.eh * nst_all + (it.stage - 1);
           bool ready = false;
           for (int spin = 0; spin < (1 << 24); ++spin) {
-            if (ld_acquire_gpu(ctr) >= kTile) { ready = true; break; }
+            if (ld_acquire_gpu(ctr) >= tph) { ready = true; break; }
             if ((spin & 255) == 255 && *abort_flag) break;
             __nanosleep(32);
           }
@@ -326,12 +337,16 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           else tma_load_5d(sA, &maps.ar_blk, full, 0, 0, it.tile, it.eh, 0);
           tma_load_5d(sB, &maps.k_blk, full, 0, 0, it.tile, h, e);
           if (three) tma_load_5d(sV, &maps.v_blk, full, 0, 0, it.tile, h, e);
-          if (has_vec) bulk_load(vec, g.cr + ((long long)it.eh * g.M + it.tile) * g.B, 512, full);
+          if (has_vec) bulk_load(vec, g.cr + ((long long)it.eh * g.M + it.tile * per) * g.B, 512, full);
         } else {
-          tma_load_5d(sA, &maps.q_col, full, 0, it.tile, 0, h, e);
+          // one box per column j of the tile: rows jj*(128/per) + l, the same row order as the blocks of
+          // a right-factor tile (a row's own columns are then the same for every lane of a warp, which
+          // the warp-wide tensor-memory loads of the softmax need)
+          for (int jj = 0; jj < per; ++jj)
+            tma_load_5d(sA + jj * (kTileBytes / per), &maps.q_col, full, 0, it.tile * per + jj, 0, h, e);
           tma_load_5d(sB, &maps.al_blk, full, 0, 0, it.tile, it.eh, 0);
           if (three) tma_load_5d(sV, &maps.y_blk, full, 0, 0, it.tile, it.eh, 0);
-          bulk_load(vec, g.cl + ((long long)it.eh * g.B + it.tile) * g.M, 512, full);
+          bulk_load(vec, g.cl + ((long long)it.eh * g.B + it.tile * per) * g.M, 512, full);
         }
         issued = n + 1;
       }
@@ -452,15 +467,23 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       const float4 st = make_float4(stp[0], stp[1], stp[2], 0.f);
       const uint32_t tmem_o = tmem + lane_base + kTmemO;
       T* dst0;
+      // Row of the tile -> (row within its block or column, which of the tile's `per` blocks / columns).
+      // Right-factor tiles hold blocks one after the other (row = blk*B + j); the accumulator of the
+      // left-factor stage (row = jj*M + m) and the column tiles of the output stage (row = jj*M + l) are
+      // indexed the same way.
+      const int rin = row & (kRowsPer - 1), rblk = row / kRowsPer;
+      long long row_y = 0;
       if (it.kind == kStageRight || it.kind == kStageRightWithV) {
-        dst0 = reinterpret_cast<T*>(g.al) + (((long long)it.eh * g.B + row) * g.M + it.tile) * kHead;
-        g.cl[((long long)it.eh * g.B + row) * g.M + it.tile] = st.z;
+        const long long rr = ((long long)it.eh * g.B + rin) * g.M + it.tile * per + rblk;
+        dst0 = reinterpret_cast<T*>(g.al) + rr * kHead;
+        g.cl[rr] = st.z;
+        row_y = rr;
       } else if (it.kind == kStageLeft) {
-        dst0 = reinterpret_cast<T*>(g.ar) + (((long long)it.eh * g.M + row) * g.B + it.tile) * kHead;
+        dst0 = reinterpret_cast<T*>(g.ar) + (((long long)it.eh * g.M + rin) * g.B + it.tile * per + rblk) * kHead;
       } else {
         const int e = it.eh / g.H, h = it.eh - e * g.H;
         dst0 = reinterpret_cast<T*>(const_cast<void*>(g.out.ptr)) + (long long)e * g.out.se + (long long)h * g.out.sh +
-               ((long long)row * g.B + it.tile) * g.out.sn;
+               ((long long)rin * g.B + it.tile * per + rblk) * g.out.sn;
       }
       // 64 accumulator columns -> one 128-byte row: both chunk loads in flight, then 4 x 32-byte stores
       // (every touched sector is written whole)
@@ -482,12 +505,11 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       if (!(dbg_flags & 4)) {
         store_row(dst0, tmem_o, st.x);
         if (it.kind == kStageRightWithV) {
-          store_row(reinterpret_cast<T*>(g.y) + (((long long)it.eh * g.B + row) * g.M + it.tile) * kHead,
-                    tmem_o + kHead, st.y);
+          store_row(reinterpret_cast<T*>(g.y) + row_y * kHead, tmem_o + kHead, st.y);
         } else if (it.kind == kStageLeft) {
           float o[32];
           tmem_ld32(tmem_o + kHead, o);
-          g.cr[((long long)it.eh * g.M + row) * g.B + it.tile] = o[0] + o[1];
+          g.cr[((long long)it.eh * g.M + rin) * g.B + it.tile * per + rblk] = o[0] + o[1];
         }
       }
       tc_fence_before();
@@ -555,7 +577,12 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
                        packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
         }
       };
-      tmem_ld32_nowait(tmem_s, ca);
+      // 64-column halves of the row this thread works on: both, or - with two blocks per tile - only the
+      // half that belongs to the row's own block or column (rows are blk*64 + j in the right-factor
+      // tiles and jj*64 + l in the column tiles; columns are blk*64 + i, or jj*64 + m); the other half of
+      // P stays zero from the start of the launch.
+      const int h0 = per > 1 ? (row >> 6) : 0, h1 = per > 1 ? h0 + 1 : 2;  // uniform within a warp
+      tmem_ld32_nowait(tmem_s + 64 * h0, ca);
       if (right) {
         auto max_chunk = [&](const float (&s)[32]) {
 #pragma unroll
@@ -567,9 +594,9 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           }
         };
 #pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
+        for (int h = h0; h < h1; ++h) {
           tmem_wait_ld(ca); tmem_ld32_nowait(tmem_s + 64 * h + 32, cb); max_chunk(ca);
-          tmem_wait_ld(cb); tmem_ld32_nowait(tmem_s + ((64 * h + 64) & 127), ca); max_chunk(cb);
+          tmem_wait_ld(cb); tmem_ld32_nowait(tmem_s + 64 * (h + 1 < h1 ? h + 1 : h0), ca); max_chunk(cb);
         }
         MA_TR(2)
         const float vmax = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
@@ -596,10 +623,10 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           store_p(packed, col0);
         };
 #pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
+        for (int h = h0; h < h1; ++h) {
           tmem_wait_ld(ca); tmem_ld32_nowait(tmem_s + 64 * h + 32, cb); exp_chunk(ca, 64 * h);
           tmem_wait_ld(cb);
-          if (h == 0) tmem_ld32_nowait(tmem_s + 64, ca);
+          if (h + 1 < h1) tmem_ld32_nowait(tmem_s + 64 * (h + 1), ca);
           else { tc_fence_before(); mbar_arrive(bar(kBarSEmpty + s3)); }  // S has been read in full
           exp_chunk(cb, 64 * h + 32);
         }
@@ -616,9 +643,9 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           }
         };
 #pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
+        for (int h = h0; h < h1; ++h) {
           tmem_wait_ld(ca); tmem_ld32_nowait(tmem_s + 64 * h + 32, cb); max_chunk(ca, vec + 64 * h);
-          tmem_wait_ld(cb); tmem_ld32_nowait(tmem_s + ((64 * h + 64) & 127), ca); max_chunk(cb, vec + 64 * h + 32);
+          tmem_wait_ld(cb); tmem_ld32_nowait(tmem_s + 64 * (h + 1 < h1 ? h + 1 : h0), ca); max_chunk(cb, vec + 64 * h + 32);
         }
         MA_TR(2)
         const float vmax = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
@@ -642,10 +669,10 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           store_p(packed, col0);
         };
 #pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
+        for (int h = h0; h < h1; ++h) {
           tmem_wait_ld(ca); tmem_ld32_nowait(tmem_s + 64 * h + 32, cb); exp_chunk(ca, vec + 64 * h, 64 * h);
           tmem_wait_ld(cb);
-          if (h == 0) tmem_ld32_nowait(tmem_s + 64, ca);
+          if (h + 1 < h1) tmem_ld32_nowait(tmem_s + 64 * (h + 1), ca);
           else { tc_fence_before(); mbar_arrive(bar(kBarSEmpty + s3)); }  // S has been read in full
           exp_chunk(cb, vec + 64 * h + 32, 64 * h + 32);
         }
@@ -735,7 +762,13 @@ cudaError_t launch_fused(const TcPlan* plan, const Geometry& g, int* counters, i
   // were issued (group-1)*128 items earlier: measured on 16 heads of N = 16384, one launch takes 365 us
   // with 1 head per group, 225 with 2, 155 with 4, 136 with 8 and 134 with 16 - below 8 the producer
   // spends its time waiting on completion counters.  8 keeps ~100 MB of state live, which still fits L2.
-  a.group = g.E * g.H < 8 ? g.E * g.H : 8;
+  // With fewer tiles per head (N = 4096: 32) the same distance in items needs more heads per group.
+  {
+    const int tiles = g.N / kTile;
+    int want = 1 + (7 * kTile + tiles - 1) / tiles;  // (want - 1) * tiles >= 7 * 128 items
+    if (want < 8) want = 8;
+    a.group = g.E * g.H < want ? g.E * g.H : want;
+  }
   a.wait_deps = wait_deps;
   a.counters = counters;
   a.dbg = 0;
@@ -743,10 +776,11 @@ cudaError_t launch_fused(const TcPlan* plan, const Geometry& g, int* counters, i
   if (const char* d = getenv("MA_B200_DEBUG")) a.dbg = atoi(d);
   if (const char* d = getenv("MA_B200_GROUP")) a.group = atoi(d) < g.E * g.H ? atoi(d) : g.E * g.H;
 #endif
-  const int total = (stage_end - stage_begin) * kTile * g.E * g.H;
+  const int total = (stage_end - stage_begin) * (g.N / kTile) * g.E * g.H;
   const int grid = total < sms ? total : sms;
-  const void* fn = plan->qk_dtype == MA_B200_BF16 ? (const void*)fused_kernel<__nv_bfloat16>
-                                                  : (const void*)fused_kernel<__half>;
+  const bool bf = plan->qk_dtype == MA_B200_BF16;
+  const void* fn = g.B == kTile ? (bf ? (const void*)fused_kernel<__nv_bfloat16, 1> : (const void*)fused_kernel<__half, 1>)
+                                : (bf ? (const void*)fused_kernel<__nv_bfloat16, 2> : (const void*)fused_kernel<__half, 2>);
   e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
   if (e != cudaSuccess) return e;
   void* params[] = {(void*)&plan->maps, (void*)&g, (void*)&a};

@@ -3,8 +3,9 @@
 // fused row softmax that reads the accumulator with tcgen05.ld (one row per thread),
 // and TMA stores of the stage result.
 //
-// Shapes served: 16-bit storage (bf16 / fp16), D = Dv = 64, block size = block count =
-// 128, N = 128*128, no mask and no padding.  Everything else runs on the generic path.
+// Shapes served by the one-tile-per-CTA kernels of this file: 16-bit storage (bf16 / fp16), D = Dv = 64,
+// block size = block count = 128, N = 128*128, no mask and no padding.  (The tensor maps built here also
+// serve the fused kernel, which takes block size = block count = 64 as well.)
 //
 // One CTA works on one 128-row tile:
 //   right-factor stages (reference: ma/ma_torch.py:10-23, :38-52): rows j of key block m
@@ -98,7 +99,8 @@ bool tc_supported(const Geometry& g, int qk_dtype, int v_dtype, const char** why
   if (qk_dtype != v_dtype || (qk_dtype != MA_B200_BF16 && qk_dtype != MA_B200_F16))
     return no("needs bf16 or f16 for q, k and v");
   if (g.D != kHead || g.Dv != kHead) return no("needs D = Dv = 64");
-  if (g.B != kTile || g.M != kTile) return no("needs block size = block count = 128");
+  if (!((g.B == kTile && g.M == kTile) || (g.B == kTile / 2 && g.M == kTile / 2)))
+    return no("needs block size = block count = 128 (or 64: two blocks per 128-row tile)");
   if (g.N != g.B * g.M) return no("needs N = block size * block count (no padding)");
   if (g.mask != nullptr) return no("mask not handled on this path");
   if ((long long)g.E * g.H > 65535) return no("E*H too large for the grid");
@@ -115,12 +117,23 @@ int tc_plan_create(const Geometry& g, int qk_dtype, TcPlan** out, const char** e
   plan->qk_dtype = qk_dtype;
   const cuuint64_t B = g.B, M = g.M, EH = (cuuint64_t)g.E * g.H;
   bool ok = true;
+  // A tile is 128 rows.  With block size 128 that is one key block (or one column j: every 128th token);
+  // with block size 64 it is two consecutive key blocks (128 consecutive tokens), or two consecutive
+  // columns j, j+1 (two boxes of 64 tokens each, rows jj*64 + l).  per = blocks / columns per tile.
+  const cuuint64_t per = kTile / B;
   auto user = [&](const View4& t, CUtensorMap* blk, CUtensorMap* col) {
-    const cuuint64_t dims[5] = {(cuuint64_t)kHead, B, M, (cuuint64_t)g.H, (cuuint64_t)g.E};
     const cuuint64_t str[4] = {(cuuint64_t)t.sn * 2, (cuuint64_t)t.sn * 2 * B, (cuuint64_t)t.sh * 2,
                                (cuuint64_t)t.se * 2};
-    if (blk) ok = ok && encode5(blk, qk_dtype, t.ptr, dims, str, kTile, 1);
-    if (col) ok = ok && encode5(col, qk_dtype, t.ptr, dims, str, 1, kTile);
+    if (blk) {  // tokens as (128, N/128)
+      const cuuint64_t bdims[5] = {(cuuint64_t)kHead, (cuuint64_t)kTile, B * M / kTile, (cuuint64_t)g.H, (cuuint64_t)g.E};
+      const cuuint64_t bstr[4] = {(cuuint64_t)t.sn * 2, (cuuint64_t)t.sn * 2 * kTile, (cuuint64_t)t.sh * 2,
+                                  (cuuint64_t)t.se * 2};
+      ok = ok && encode5(blk, qk_dtype, t.ptr, bdims, bstr, kTile, 1);
+    }
+    if (col) {  // tokens as (B, M): one column j, 128 / per blocks (a tile takes `per` such boxes)
+      const cuuint64_t dims[5] = {(cuuint64_t)kHead, B, M, (cuuint64_t)g.H, (cuuint64_t)g.E};
+      ok = ok && encode5(col, qk_dtype, t.ptr, dims, str, 1, (cuuint32_t)(kTile / per));
+    }
   };
   user(g.q, &plan->maps.q_blk, &plan->maps.q_col);
   user(g.k, &plan->maps.k_blk, nullptr);
@@ -131,8 +144,12 @@ int tc_plan_create(const Geometry& g, int qk_dtype, TcPlan** out, const char** e
     const cuuint64_t dims[5] = {(cuuint64_t)kHead, inner, outer, EH, 1};
     const cuuint64_t str[4] = {(cuuint64_t)kHead * 2, (cuuint64_t)kHead * 2 * inner,
                                (cuuint64_t)kHead * 2 * inner * outer, (cuuint64_t)kHead * 2 * inner * outer * EH};
-    ok = ok && encode5(blk, qk_dtype, base, dims, str, kTile, 1);
-    ok = ok && encode5(col, qk_dtype, base, dims, str, 1, kTile);
+    // rows of a head as (128, inner*outer/128): a tile is 128 consecutive rows whatever the block size
+    const cuuint64_t bdims[5] = {(cuuint64_t)kHead, (cuuint64_t)kTile, inner * outer / kTile, EH, 1};
+    const cuuint64_t bstr[4] = {(cuuint64_t)kHead * 2, (cuuint64_t)kHead * 2 * kTile,
+                                (cuuint64_t)kHead * 2 * inner * outer, (cuuint64_t)kHead * 2 * inner * outer * EH};
+    ok = ok && encode5(blk, qk_dtype, base, bdims, bstr, kTile, 1);
+    ok = ok && encode5(col, qk_dtype, base, dims, str, 1, (cuuint32_t)(kTile / per));
   };
   if (g.T > 1) scratch(g.ar, B, M, &plan->maps.ar_blk, &plan->maps.ar_col);
   else { plan->maps.ar_blk = plan->maps.q_blk; plan->maps.ar_col = plan->maps.q_col; }

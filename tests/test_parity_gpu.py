@@ -102,6 +102,20 @@ TC_CASES = [c for c in CASES if c["B"] == 128 and c["N"] == 16384 and c["dtype"]
 
 
 TC_IMPLS = ["b200-tcgen05", "b200-tcgen05-staged", "b200-tcgen05-tile"]
+# block size 64 (two blocks per 128-row tile): the fused kernel only
+TC64_CASES = [c for c in CASES if c["B"] == 64 and c["N"] == 4096 and c["dtype"] in ("bf16", "f16")]
+
+
+@pytest.mark.parametrize("impl", ["b200-tcgen05", "b200-tcgen05-staged"])
+@pytest.mark.parametrize("case", TC64_CASES, ids=[c["name"] for c in TC64_CASES])
+def test_fused_kernel_with_two_blocks_per_tile(ma, case, impl):
+    q, k, v, mask = make_inputs(case)
+    out = _run(ma, case, impl, q, k, v, mask)
+    ref = monarch_attention_oracle(q, k, v, mask, case["T"], case["B"], case["pre_pad"])
+    vd = case["vdtype"]
+    check_close(out.double().cpu().numpy(), ref.double().numpy(), vd, case["name"] + " vs oracle")
+    check_close(bits_to_float(sample_of(out), vd), bits_to_float(golden_sample(case["name"]), vd), vd,
+                case["name"] + " vs reference golden")
 
 
 @pytest.mark.parametrize("impl", TC_IMPLS)
@@ -149,7 +163,8 @@ def _state_from_workspace(ma, q, k, v, T, B, kernel):
                                          ("cfg3_n4096_unit_bf16", 1), ("edge_t4_f32", 1),
                                          ("cfg3_n4096_unit_bf16", 5), ("cfg3_n16384_unit_bf16", 5),
                                          ("cfg5_dit_bf16", 5), ("edge_full_block_masked_t3_bf16", 5),
-                                         ("cfg3_n65536_bf16", 5), ("edge_b136_m40_f16", 5)])
+                                         ("cfg3_n65536_bf16", 5), ("edge_b136_m40_f16", 5),
+                                         ("cfg3_n4096_unit_bf16", 2), ("cfg3_n4096_unit_bf16", 3)])
 def test_stage_state_matches_oracle(ma, name, kernel):
     """Every stage-to-stage tensor (ar, cr, al, cl, y), not just the final output."""
     case = CASES_BY_NAME[name]
