@@ -58,8 +58,6 @@ enum { MA_B200_F32 = 0, MA_B200_BF16 = 1, MA_B200_F16 = 2 };
  *   TCGEN05        persistent tcgen05 kernel, all 2T stages in one launch: 16-bit inputs,
  *                  D = Dv = 64, no mask, no padding, block size = block count = 128 or 64
  *   TCGEN05_STAGED the same kernel launched once per stage (for per-stage timing)
- *   TCGEN05_TILE   one-tile-per-CTA tcgen05 stage kernels, block size 128 only
- *                  (2T launches; cross-check)
  *   WARP_MMA       warp-level tensor-core stage kernels for 16-bit inputs with block size and
  *                  block count up to 256 and D <= 80 (D <= 64 when either exceeds 128)
  *                  (2T launches; masks and padding handled)
@@ -70,8 +68,7 @@ enum {
   MA_B200_KERNEL_AUTO = 0,
   MA_B200_KERNEL_GENERIC = 1,
   MA_B200_KERNEL_TCGEN05 = 2,
-  MA_B200_KERNEL_TCGEN05_STAGED = 3,
-  MA_B200_KERNEL_TCGEN05_TILE = 4,
+  MA_B200_KERNEL_TCGEN05_STAGED = 3, /* (4 is not in use) */
   MA_B200_KERNEL_WARP_MMA = 5,
   MA_B200_KERNEL_HEAD_FUSED = 6
 };
@@ -138,6 +135,24 @@ MA_B200_API int ma_b200_forward_timed(const ma_b200_problem* p, void* workspace,
 /* Synchronise `stream` and read the device-side status flag of the last forward that used
  * this workspace: MA_B200_OK or MA_B200_DEVICE_WAIT_EXPIRED. */
 MA_B200_API int ma_b200_device_status(void* workspace, void* stream);
+
+/* Without synchronising anything: has a bounded wait of the fused tcgen05 kernel given up on `device`
+ * since the last poll?  A CTA that gives up stores its code in a page-locked host word the library
+ * maps once per device (at the first fused launch there), so the answer trails the GPU by at most
+ * the kernels still in flight.  MA_B200_OK, or MA_B200_DEVICE_WAIT_EXPIRED once per incident (the
+ * word is cleared by the poll).  This is the lazily read error flag of the eager call: the reference
+ * raises from inside the call (ma/monarch_attention.py:50-59), an asynchronous launch cannot.
+ * No counterpart in the reference. */
+MA_B200_API int ma_b200_poll_device_status(int device);
+
+/* Self-test of the give-up path (no counterpart in the reference): launches the left-factor stage of
+ * `p` (num_steps >= 2, a problem the fused kernel takes) alone, with the completion counters it waits
+ * on left at zero and a short patience, so that every CTA's bounded wait runs out and the kernel
+ * returns by itself after a few hundred microseconds.  Afterwards ma_b200_device_status(workspace)
+ * and ma_b200_poll_device_status() report MA_B200_DEVICE_WAIT_EXPIRED, and the next ordinary call is
+ * unaffected.  Nothing faults, traps or spins without bound. */
+MA_B200_API int ma_b200_selftest_wait_expiry(const ma_b200_problem* p, void* workspace, size_t workspace_bytes,
+                                             void* stream);
 
 /* Human-readable text for a return code. */
 MA_B200_API const char* ma_b200_status_string(int status);

@@ -10,9 +10,9 @@ import os
 
 ABI_VERSION = 1
 F32, BF16, F16 = 0, 1, 2
-KERNEL_AUTO, KERNEL_GENERIC, KERNEL_TCGEN05, KERNEL_TCGEN05_STAGED, KERNEL_TCGEN05_TILE, KERNEL_WARP_MMA, KERNEL_HEAD_FUSED = 0, 1, 2, 3, 4, 5, 6
+KERNEL_AUTO, KERNEL_GENERIC, KERNEL_TCGEN05, KERNEL_TCGEN05_STAGED, KERNEL_WARP_MMA, KERNEL_HEAD_FUSED = 0, 1, 2, 3, 5, 6
 KERNEL_NAMES = {KERNEL_AUTO: "auto", KERNEL_GENERIC: "generic", KERNEL_TCGEN05: "tcgen05-fused",
-                KERNEL_TCGEN05_STAGED: "tcgen05-staged", KERNEL_TCGEN05_TILE: "tcgen05-tile",
+                KERNEL_TCGEN05_STAGED: "tcgen05-staged",
                 KERNEL_WARP_MMA: "warp-mma", KERNEL_HEAD_FUSED: "head-fused"}
 OK, INVALID_ARGUMENT, UNSUPPORTED, CUDA_ERROR, DEVICE_WAIT_EXPIRED, WORKSPACE_TOO_SMALL = range(6)
 
@@ -23,6 +23,7 @@ EXPORTS = (
     "ma_b200_device_status", "ma_b200_status_string", "ma_b200_last_error", "ma_b200_abi_version",
     "ma_b200_forward_static_scratch", "ma_b200_static_scratch_bytes", "ma_b200_static_scratch_last_error",
     "ma_b200_host_scratch_bytes", "ma_b200_forward_host", "ma_b200_host_last_error",
+    "ma_b200_poll_device_status", "ma_b200_selftest_wait_expiry",
 )
 
 
@@ -70,6 +71,10 @@ def load() -> C.CDLL:
     lib.ma_b200_forward_timed.restype = C.c_int
     lib.ma_b200_device_status.argtypes = [C.c_void_p, C.c_void_p]
     lib.ma_b200_device_status.restype = C.c_int
+    lib.ma_b200_poll_device_status.argtypes = [C.c_int]
+    lib.ma_b200_poll_device_status.restype = C.c_int
+    lib.ma_b200_selftest_wait_expiry.argtypes = [pp, C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.ma_b200_selftest_wait_expiry.restype = C.c_int
     lib.ma_b200_status_string.argtypes = [C.c_int]
     lib.ma_b200_status_string.restype = C.c_char_p
     lib.ma_b200_last_error.argtypes = []

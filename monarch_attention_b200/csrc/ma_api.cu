@@ -8,6 +8,7 @@
 #include <string>
 
 #include "ma_common.cuh"
+#include "ma_tc_plan.cuh"
 
 namespace {
 
@@ -41,7 +42,7 @@ int validate(const ma_b200_problem* p, bool need_pointers) {
     return fail(MA_B200_INVALID_ARGUMENT, "unknown dtype");
   if (!(p->qk_dtype == p->v_dtype || p->v_dtype == MA_B200_F32))
     return fail(MA_B200_UNSUPPORTED, "v_dtype must equal qk_dtype or be f32");
-  if (p->kernel < MA_B200_KERNEL_AUTO || p->kernel > MA_B200_KERNEL_HEAD_FUSED)
+  if (p->kernel < MA_B200_KERNEL_AUTO || p->kernel > MA_B200_KERNEL_HEAD_FUSED || p->kernel == 4)
     return fail(MA_B200_INVALID_ARGUMENT, "unknown kernel family");
   if ((long long)p->E * p->H > 0x7fffffffLL / 2) return fail(MA_B200_INVALID_ARGUMENT, "E*H too large");
   if (need_pointers) {
@@ -86,11 +87,9 @@ ma::Geometry make_geometry(const ma_b200_problem* p) {
 int resolve_kernel(const ma_b200_problem* p, const ma::Geometry& g, int* kernel) {
   const char* why = "";
   const bool tc_ok = ma::tc_supported(g, p->qk_dtype, p->v_dtype, &why);
-  const bool wants_tc = p->kernel >= MA_B200_KERNEL_TCGEN05 && p->kernel <= MA_B200_KERNEL_TCGEN05_TILE;
+  const bool wants_tc = p->kernel == MA_B200_KERNEL_TCGEN05 || p->kernel == MA_B200_KERNEL_TCGEN05_STAGED;
   if (wants_tc && !tc_ok)
     return fail(MA_B200_UNSUPPORTED, std::string("tcgen05 path cannot run this problem: ") + why);
-  if (p->kernel == MA_B200_KERNEL_TCGEN05_TILE && g.B != 128)
-    return fail(MA_B200_UNSUPPORTED, "one-tile-per-CTA tcgen05 kernels need block size = block count = 128");
   const char* why_w = "";
   const bool warp_ok = ma::warp_supported(g, p->qk_dtype, p->v_dtype, &why_w);
   if (p->kernel == MA_B200_KERNEL_WARP_MMA && !warp_ok)
@@ -108,7 +107,7 @@ int resolve_kernel(const ma_b200_problem* p, const ma::Geometry& g, int* kernel)
     const size_t need = ma::generic_stage_smem_bytes(g, g.B > g.M ? ma::kStageRight : ma::kStageLeft);
     if (need > 200 * 1024)
       return fail(MA_B200_UNSUPPORTED, "generic path: block size or block count too large for shared memory");
-    if (g.M > 65535 || g.B > 65535 || (long long)g.E * g.H > 65535LL * 32768)
+    if (g.M > 65535 || g.B > 65535)  // gridDim.y; E*H sits on gridDim.x (limit 2^31 - 1, checked in validate)
       return fail(MA_B200_UNSUPPORTED, "generic path: grid too large");
   }
   return MA_B200_OK;
@@ -168,11 +167,13 @@ int run_forward(const ma_b200_problem* p, void* workspace, size_t workspace_byte
   if (ce != cudaSuccess) return cuda_fail(ce, "cudaMemsetAsync(status, counters)");
   int* counters = reinterpret_cast<int*>(ws + L.counters);
 
-  ma::TcPlan* plan = nullptr;
-  if (L.kernel >= MA_B200_KERNEL_TCGEN05 && L.kernel <= MA_B200_KERNEL_TCGEN05_TILE) {
+  ma::TcPlan plan_store;
+  const ma::TcPlan* plan = nullptr;
+  if (L.kernel == MA_B200_KERNEL_TCGEN05 || L.kernel == MA_B200_KERNEL_TCGEN05_STAGED) {
     const char* err = "";
-    rc = ma::tc_plan_create(g, p->qk_dtype, &plan, &err);
+    rc = ma::tc_plan_get(g, p->qk_dtype, &plan_store, &err);
     if (rc != MA_B200_OK) return fail(rc, std::string("tcgen05 plan: ") + err);
+    plan = &plan_store;
   }
 
   const int n_stages = 2 * p->num_steps;
@@ -185,8 +186,7 @@ int run_forward(const ma_b200_problem* p, void* workspace, size_t workspace_byte
   int stage_idx = 0;
   auto launch = [&](ma::StageKind kind, bool first) -> cudaError_t {
     cudaError_t e;
-    if (L.kernel == MA_B200_KERNEL_TCGEN05_TILE) e = ma::launch_tc_stage(plan, g, kind, first, stream);
-    else if (L.kernel == MA_B200_KERNEL_TCGEN05_STAGED)
+    if (L.kernel == MA_B200_KERNEL_TCGEN05_STAGED)
       e = ma::launch_fused(plan, g, counters, stage_idx, stage_idx + 1, 0, stream);
     else if (L.kernel == MA_B200_KERNEL_WARP_MMA) e = ma::launch_warp_stage(g, p->qk_dtype, kind, first, stream);
     else e = ma::launch_generic_stage(g, p->qk_dtype, p->v_dtype, kind, first, stream);
@@ -231,7 +231,6 @@ int run_forward(const ma_b200_problem* p, void* workspace, size_t workspace_byte
     for (int i = 0; i <= n_stages; ++i) cudaEventDestroy(ev[i]);
     delete[] ev;
   }
-  if (plan != nullptr) ma::tc_plan_destroy(plan);
   return rc;
 }
 
@@ -269,6 +268,46 @@ int ma_b200_device_status(void* workspace, void* stream) {
   if (ce != cudaSuccess) return fail(MA_B200_CUDA_ERROR, std::string("device_status: ") + cudaGetErrorString(ce));
   if (flag != 0)
     return fail(MA_B200_DEVICE_WAIT_EXPIRED, "device flag = " + std::to_string(flag) + " (a bounded wait expired)");
+  return MA_B200_OK;
+}
+
+int ma_b200_poll_device_status(int device) {
+  const int code = ma::fused_poll_status(device);
+  if (code != 0)
+    return fail(MA_B200_DEVICE_WAIT_EXPIRED, "device " + std::to_string(device) + ": wait " + std::to_string(code) +
+                                                 " of the fused kernel gave up; the output of that call is undefined");
+  return MA_B200_OK;
+}
+
+int ma_b200_selftest_wait_expiry(const ma_b200_problem* p, void* workspace, size_t workspace_bytes, void* stream_v) {
+  int rc = validate(p, true);
+  if (rc != MA_B200_OK) return rc;
+  ma_b200_problem q = *p;
+  q.kernel = MA_B200_KERNEL_TCGEN05;
+  ma_b200_workspace_layout L;
+  rc = layout_of(&q, &L);
+  if (rc != MA_B200_OK) return rc;
+  if (workspace == nullptr || reinterpret_cast<uintptr_t>(workspace) % 256 != 0 || workspace_bytes < L.total)
+    return fail(MA_B200_INVALID_ARGUMENT, "workspace is NULL, misaligned or too small");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  ma::Geometry g = make_geometry(&q);
+  char* ws = reinterpret_cast<char*>(workspace);
+  g.status = reinterpret_cast<int*>(ws + L.status);
+  g.ar = ws + L.ar; g.cr = reinterpret_cast<float*>(ws + L.cr);
+  g.al = ws + L.al; g.cl = reinterpret_cast<float*>(ws + L.cl);
+  g.y = ws + L.y;
+  cudaError_t ce = cudaMemsetAsync(ws + L.status, 0, L.ar - L.status, stream);
+  if (ce != cudaSuccess) return fail(MA_B200_CUDA_ERROR, cudaGetErrorString(ce));
+  ma::TcPlan plan;
+  const char* err = "";
+  rc = ma::tc_plan_get(g, q.qk_dtype, &plan, &err);
+  if (rc != MA_B200_OK) return fail(rc, std::string("tcgen05 plan: ") + err);
+  // Stage 1 alone, waiting on completion counters of stage 0 that nothing will ever raise: every
+  // producer runs out of patience after a few hundred microseconds and the CTAs return.
+  ma::fused_set_spin_limit(4096);
+  ce = ma::launch_fused(&plan, g, reinterpret_cast<int*>(ws + L.counters), 1, 2, 1, stream);
+  ma::fused_set_spin_limit(0);
+  if (ce != cudaSuccess) return fail(MA_B200_CUDA_ERROR, std::string("fused kernel: ") + cudaGetErrorString(ce));
   return MA_B200_OK;
 }
 

@@ -80,14 +80,20 @@ cudaError_t launch_head_fused(const Geometry& g, int qk_dtype, cudaStream_t stre
 
 // Tensor-core (tcgen05) path.
 bool tc_supported(const Geometry& g, int qk_dtype, int v_dtype, const char** why);
-// Prepares per-call tensor maps; returns an opaque plan used by launch_tc_stage.
+// The TMA tensor maps of one call.  tc_plan_get copies them into *plan, from a cache when the same
+// pointers, strides and sizes were seen before; tc_plan_create always encodes (heap object).
 struct TcPlan;
+int tc_plan_get(const Geometry& g, int qk_dtype, TcPlan* plan, const char** err);
 int tc_plan_create(const Geometry& g, int qk_dtype, TcPlan** plan, const char** err);
 void tc_plan_destroy(TcPlan* plan);
-cudaError_t launch_tc_stage(const TcPlan* plan, const Geometry& g, StageKind kind, bool first, cudaStream_t stream);
 // Persistent fused kernel: stages [stage_begin, stage_end) of the 2T stages in one cooperative launch.
 size_t fused_counter_bytes(const Geometry& g);
 cudaError_t launch_fused(const TcPlan* plan, const Geometry& g, int* counters, int stage_begin, int stage_end,
                          int wait_deps, cudaStream_t stream);
+// Code of a bounded device-side wait that gave up on `device` since the last poll (0 = none); reads a mapped
+// host word, so it needs no synchronisation.
+int fused_poll_status(int device);
+// Iterations of the producer's dependency wait before it gives up (0 = default); for the wait-expiry self-test.
+void fused_set_spin_limit(int iterations);
 
 }  // namespace ma

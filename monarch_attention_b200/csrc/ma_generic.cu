@@ -99,7 +99,7 @@ template <typename TQ, typename TV, bool WITH_V>
 __global__ void __launch_bounds__(kThreads) right_stage_kernel(const Geometry g, const int first, const int staged) {
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m = blockIdx.x, eh = blockIdx.y;
+  const int m = blockIdx.y, eh = blockIdx.x;  // E*H on x: no 65535 limit
   const int e = eh / g.H, h = eh % g.H;
   const int B = g.B, D = g.D, Dv = g.Dv, M = g.M;
   float* avec = smem + warp * (D + B);
@@ -208,7 +208,7 @@ template <typename TQ>
 __global__ void __launch_bounds__(kThreads) left_stage_kernel(const Geometry g, const int staged) {
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int j = blockIdx.x, eh = blockIdx.y;
+  const int j = blockIdx.y, eh = blockIdx.x;
   const int e = eh / g.H, h = eh % g.H;
   const int B = g.B, D = g.D, M = g.M;
   float* avec = smem + warp * (D + M);
@@ -304,7 +304,7 @@ template <typename TQ, typename TV>
 __global__ void __launch_bounds__(kThreads) output_stage_kernel(const Geometry g, const int staged) {
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int j = blockIdx.x, eh = blockIdx.y;
+  const int j = blockIdx.y, eh = blockIdx.x;
   const int e = eh / g.H, h = eh % g.H;
   const int B = g.B, D = g.D, Dv = g.Dv, M = g.M;
   float* avec = smem + warp * (D + M);
@@ -397,19 +397,19 @@ cudaError_t launch_typed(const Geometry& g, StageKind kind, bool first, cudaStre
   switch (kind) {
     case kStageRight:
       if ((err = raise((const void*)right_stage_kernel<TQ, TV, false>)) != cudaSuccess) return err;
-      right_stage_kernel<TQ, TV, false><<<dim3(g.M, EH), block, smem, stream>>>(g, first ? 1 : 0, staged);
+      right_stage_kernel<TQ, TV, false><<<dim3(EH, g.M), block, smem, stream>>>(g, first ? 1 : 0, staged);
       break;
     case kStageRightWithV:
       if ((err = raise((const void*)right_stage_kernel<TQ, TV, true>)) != cudaSuccess) return err;
-      right_stage_kernel<TQ, TV, true><<<dim3(g.M, EH), block, smem, stream>>>(g, first ? 1 : 0, staged);
+      right_stage_kernel<TQ, TV, true><<<dim3(EH, g.M), block, smem, stream>>>(g, first ? 1 : 0, staged);
       break;
     case kStageLeft:
       if ((err = raise((const void*)left_stage_kernel<TQ>)) != cudaSuccess) return err;
-      left_stage_kernel<TQ><<<dim3(g.B, EH), block, smem, stream>>>(g, staged);
+      left_stage_kernel<TQ><<<dim3(EH, g.B), block, smem, stream>>>(g, staged);
       break;
     case kStageOutput:
       if ((err = raise((const void*)output_stage_kernel<TQ, TV>)) != cudaSuccess) return err;
-      output_stage_kernel<TQ, TV><<<dim3(g.B, EH), block, smem, stream>>>(g, staged);
+      output_stage_kernel<TQ, TV><<<dim3(EH, g.B), block, smem, stream>>>(g, staged);
       break;
   }
   return cudaGetLastError();

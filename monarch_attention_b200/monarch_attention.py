@@ -124,7 +124,14 @@ def monarch_attention_b200(q: Tensor, k: Tensor, v: Tensor, attn_mask: Tensor | 
     (reference: experiments/vit/model.py:99-101), which then costs nothing.
     """
     _check_inputs(q, k, v, attn_mask)
+    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+        raise RuntimeError("monarch_attention_b200 is forward-only: call it under torch.no_grad() or on detached "
+                           "tensors (the reference's impl=\"torch\" is the differentiable path)")
     lib = _cabi.load()
+    dev_index = q.device.index if q.device.index is not None else torch.cuda.current_device()
+    # A bounded wait of an earlier asynchronous call on this device that gave up is reported here, at the
+    # next call, without a synchronisation (the kernel leaves its code in mapped host memory).
+    _cabi.raise_for_status(lib.ma_b200_poll_device_status(dev_index))
     q, k, v = _unit_inner(q), _unit_inner(k), _unit_inner(v)
     E, H, N, _ = q.shape
     if out is None:
@@ -170,8 +177,6 @@ register_impl("b200-warp-mma",
               lambda q, k, v, m, T, B, pp: monarch_attention_b200(q, k, v, m, T, B, pp, kernel=_cabi.KERNEL_WARP_MMA))
 register_impl("b200-head-fused",
               lambda q, k, v, m, T, B, pp: monarch_attention_b200(q, k, v, m, T, B, pp, kernel=_cabi.KERNEL_HEAD_FUSED))
-register_impl("b200-tcgen05-tile",
-              lambda q, k, v, m, T, B, pp: monarch_attention_b200(q, k, v, m, T, B, pp, kernel=_cabi.KERNEL_TCGEN05_TILE))
 
 
 class MonarchAttention(nn.Module):
@@ -179,8 +184,8 @@ class MonarchAttention(nn.Module):
 
     ``impl`` selects the kernel family: "b200" (default: fused tensor-core kernel when the
     problem fits it, otherwise the generic path), "b200-generic", "b200-tcgen05" (fused, one
-    launch), "b200-tcgen05-staged" (same kernel, one launch per stage), "b200-tcgen05-tile"
-    (one tile per CTA), "b200-warp-mma" (warp-level tensor-core kernels for small blocks) or
+    launch), "b200-tcgen05-staged" (same kernel, one launch per stage),
+    "b200-warp-mma" (warp-level tensor-core kernels for small blocks) or
     "b200-head-fused" (one CTA per head, one iteration, state in shared memory).  The reference's
     "torch" and "triton" implementations are not part of this library; asking for an
     unknown name raises ``ValueError`` exactly as the reference does.

@@ -79,6 +79,28 @@ def _config_cases():
         _c("cfg3_n16384_unit_bf16", 1, 1, 16384, 64, 128, 2, False, "bf16", scale="unit"),
         _c("cfg3_n4096_f16", 1, 1, 4096, 64, 64, 2, False, "f16", scale="unit"),
         _c("cfg3_n4096_f32", 1, 1, 4096, 64, 64, 2, False, "f32", scale="unit"),
+        # the fused tensor-core kernel's other stage sequences (one iteration: no left-factor stage; three
+        # and four: right-factor stages that read ar / cr), sharp logits, fp16 at block size 128, and head
+        # counts that leave a partial last head group (12 heads in groups of 8; 33 heads of 4096 tokens)
+        _c("cfg3_n16384_t1_bf16", 1, 1, 16384, 64, 128, 1, False, "bf16", scale="rsqrt_d"),
+        _c("cfg3_n16384_t1_unit_bf16", 1, 1, 16384, 64, 128, 1, False, "bf16", scale="unit"),
+        _c("cfg3_n16384_t3_bf16", 1, 1, 16384, 64, 128, 3, False, "bf16", scale="rsqrt_d"),
+        _c("cfg3_n16384_t3_unit_bf16", 1, 1, 16384, 64, 128, 3, False, "bf16", scale="unit"),
+        _c("cfg3_n16384_t4_bf16", 1, 1, 16384, 64, 128, 4, False, "bf16", scale="rsqrt_d"),
+        _c("cfg3_n16384_t4_unit_bf16", 1, 1, 16384, 64, 128, 4, False, "bf16", scale="unit"),
+        _c("cfg3_n16384_act_bf16", 1, 1, 16384, 64, 128, 2, False, "bf16", scale="activations"),
+        _c("cfg3_n16384_t3_act_bf16", 1, 1, 16384, 64, 128, 3, False, "bf16", scale="activations"),
+        _c("cfg3_n16384_unit_f16", 1, 1, 16384, 64, 128, 2, False, "f16", scale="unit"),
+        _c("cfg3_n16384_t3_act_f16", 1, 1, 16384, 64, 128, 3, False, "f16", scale="activations"),
+        _c("cfg3_n16384_e2h6_bf16", 2, 6, 16384, 64, 128, 2, False, "bf16", scale="rsqrt_d"),
+        _c("cfg3_n4096_t1_bf16", 1, 2, 4096, 64, 64, 1, False, "bf16", scale="rsqrt_d"),
+        _c("cfg3_n4096_t1_unit_bf16", 1, 2, 4096, 64, 64, 1, False, "bf16", scale="unit"),
+        _c("cfg3_n4096_t3_bf16", 1, 2, 4096, 64, 64, 3, False, "bf16", scale="rsqrt_d"),
+        _c("cfg3_n4096_t3_unit_bf16", 1, 2, 4096, 64, 64, 3, False, "bf16", scale="unit"),
+        _c("cfg3_n4096_t4_unit_bf16", 1, 2, 4096, 64, 64, 4, False, "bf16", scale="unit"),
+        _c("cfg3_n4096_act_bf16", 1, 2, 4096, 64, 64, 2, False, "bf16", scale="activations"),
+        _c("cfg3_n4096_t3_act_f16", 1, 2, 4096, 64, 64, 3, False, "f16", scale="activations"),
+        _c("cfg3_n4096_h33_bf16", 1, 33, 4096, 64, 64, 2, False, "bf16", scale="unit"),
         _c("cfg3_n65536_bf16", 1, 1, 65536, 64, 256, 2, False, "bf16", scale="activations"),
         _c("cfg3_n65536_unit_f16", 1, 1, 65536, 64, 256, 2, False, "f16", scale="unit"),
         # config 4 (RoBERTa): right padding produces fully masked key blocks

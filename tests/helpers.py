@@ -47,17 +47,18 @@ def error_metrics(got, ref):
     return float(np.abs(d).max()), float(np.abs(d).max() / scale), fro
 
 
-# Tolerances.  fp32: 1e-4 relative (max-abs error over max-abs reference, and
-# relative Frobenius).  bf16: 2e-2 max-abs, plus a relative Frobenius bound
-# because max-abs alone is vacuous for small-magnitude outputs.  fp16: the
-# reference's own test tolerance of 1e-2 (ma/tests/test_ma.py:64-65) plus a
-# relative Frobenius bound.  The max-abs bounds are stated for outputs of unit
-# scale; where the reference output exceeds 1 in magnitude they scale with
-# max|ref| (one bf16 ulp at 3.0 is already 1.6e-2, so a single rounding flip
-# would otherwise fail the absolute bound).
+# Tolerances against the reference's eager implementation on the same inputs.
+# fp32: 1e-4 relative (max-abs error over max-abs reference, and relative Frobenius).
+# bf16: 2e-2 max-abs and relative Frobenius 1e-2 (max-abs alone is vacuous for small-magnitude
+# outputs).  fp16: the reference's own test tolerance of 1e-2 (ma/tests/test_ma.py:64-65) and relative
+# Frobenius 4e-3.  The max-abs bounds are absolute for outputs of magnitude up to 1; where the
+# reference output exceeds 1 they scale with max|ref|, because there a single rounding flip of the
+# 16-bit result already moves an element by more than the bound (one bf16 ulp in [2, 4) is 1.6e-2);
+# test_fused_kernel_is_no_further_from_float64_than_the_reference shows that this allowance is
+# not hiding an error of the kernels.
 TOL = {
     "f32": dict(max_abs=None, rel_max=1e-4, fro=1e-4),
-    "bf16": dict(max_abs=2e-2, rel_max=None, fro=1.5e-2),
+    "bf16": dict(max_abs=2e-2, rel_max=None, fro=1e-2),
     "f16": dict(max_abs=1e-2, rel_max=None, fro=4e-3),
 }
 

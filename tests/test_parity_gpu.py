@@ -8,7 +8,7 @@ import torch
 
 from helpers import (CASES, CASES_BY_NAME, DTYPES, bits_to_float, check_close, error_metrics, golden_sample,
                      make_inputs, sample_of)
-from oracle.monarch_oracle import OracleState, monarch_attention_oracle
+from oracle.monarch_oracle import OracleState, monarch_attention_dense_f64, monarch_attention_oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -101,7 +101,7 @@ def test_default_kernel_choice_matches_oracle(ma, case):
 TC_CASES = [c for c in CASES if c["B"] == 128 and c["N"] == 16384 and c["dtype"] in ("bf16", "f16")]
 
 
-TC_IMPLS = ["b200-tcgen05", "b200-tcgen05-staged", "b200-tcgen05-tile"]
+TC_IMPLS = ["b200-tcgen05", "b200-tcgen05-staged"]
 # block size 64 (two blocks per 128-row tile): the fused kernel only
 TC64_CASES = [c for c in CASES if c["B"] == 64 and c["N"] == 4096 and c["dtype"] in ("bf16", "f16")]
 
@@ -159,7 +159,12 @@ def _state_from_workspace(ma, q, k, v, T, B, kernel):
 
 
 @pytest.mark.parametrize("name,kernel", [("cfg3_n16384_unit_bf16", 2), ("cfg3_n16384_unit_bf16", 3),
-                                         ("cfg3_n16384_unit_bf16", 4), ("cfg3_n16384_unit_bf16", 1),
+                                         ("cfg3_n16384_unit_bf16", 1),
+                                         ("cfg3_n16384_t1_unit_bf16", 2), ("cfg3_n16384_t3_unit_bf16", 2),
+                                         ("cfg3_n16384_t3_act_bf16", 2), ("cfg3_n16384_t4_unit_bf16", 3),
+                                         ("cfg3_n16384_unit_f16", 2), ("cfg3_n16384_t3_act_f16", 2),
+                                         ("cfg3_n4096_t1_unit_bf16", 2), ("cfg3_n4096_t3_unit_bf16", 2),
+                                         ("cfg3_n4096_t3_act_f16", 2), ("cfg3_n4096_act_bf16", 3),
                                          ("cfg3_n4096_unit_bf16", 1), ("edge_t4_f32", 1),
                                          ("cfg3_n4096_unit_bf16", 5), ("cfg3_n16384_unit_bf16", 5),
                                          ("cfg5_dit_bf16", 5), ("edge_full_block_masked_t3_bf16", 5),
@@ -175,7 +180,7 @@ def test_stage_state_matches_oracle(ma, name, kernel):
     out, st, L = _state_from_workspace(ma, q.to(dev), k.to(dev), v.to(dev), case["T"], case["B"], kernel)
     assert L.kernel == kernel
     dt = case["dtype"]
-    fro_lim = {"f32": 1e-4, "bf16": 1.5e-2, "f16": 4e-3}[dt]
+    fro_lim = {"f32": 1e-4, "bf16": 1e-2, "f16": 4e-3}[dt]
     report = {}
     for key in ("ar", "cr", "al", "cl", "y"):
         want = getattr(st_ref, key)
@@ -240,7 +245,7 @@ def test_get_matrix_is_row_stochastic_and_matches_oracle(ma):
     assert a.dtype == torch.float32 and a.shape == (1, 2, 36, 36)
     assert torch.allclose(a.sum(-1), torch.ones_like(a.sum(-1)), atol=1e-3)
     ref = monarch_attention_oracle(q, k, v, None, case["T"], case["B"], False)
-    assert error_metrics(a.double().cpu().numpy(), ref.double().numpy())[2] < 1.5e-2
+    assert error_metrics(a.double().cpu().numpy(), ref.double().numpy())[2] < 1e-2
 
 
 def test_module_errors_on_gpu(ma):
@@ -253,6 +258,60 @@ def test_module_errors_on_gpu(ma):
         mod(q, q, q, torch.ones(1, 31, device=dev))
     with pytest.raises(ValueError, match="tcgen05 path cannot run"):
         ma.MonarchAttention(8, 2, "post", impl="b200-tcgen05")(q.half(), q.half(), q.half())
+
+
+@pytest.mark.parametrize("name", ["cfg3_n16384_act_bf16", "cfg3_n16384_t3_act_bf16", "cfg3_n4096_act_bf16",
+                                  "cfg3_n16384_t3_act_f16"])
+def test_fused_kernel_is_no_further_from_float64_than_the_reference(ma, name):
+    """On sharp logits the 16-bit reference is itself ~1e-2 away from exact arithmetic.  The fused kernel
+    keeps the reference's rounding points, so it must sit as close to the float64 restatement as the
+    reference's own 16-bit result does - the tolerance versus the reference is not hiding an error."""
+    case = CASES_BY_NAME[name]
+    q, k, v, _ = make_inputs(case)
+    q, k, v = q[:, :1], k[:, :1], v[:, :1]   # one head keeps the float64 loops short
+    exact = monarch_attention_dense_f64(q.double().numpy(), k.double().numpy(), v.double().numpy(), None,
+                                        case["T"], case["B"], False)
+    ref = monarch_attention_oracle(q, k, v, None, case["T"], case["B"], False).double().numpy()
+    out = _run(ma, case, "b200-tcgen05", q, k, v, None).double().cpu().numpy()
+    err_ref, err_out = error_metrics(ref, exact)[2], error_metrics(out, exact)[2]
+    assert err_out <= 1.25 * err_ref + 1e-4, f"{name}: kernel vs f64 {err_out:.3e}, reference vs f64 {err_ref:.3e}"
+
+
+def test_expired_device_wait_is_reported_and_harmless(ma):
+    """A bounded wait that runs out must end the launch by itself, set the status word, be raised by the
+    next call through the module API, and leave the library usable.  The wait is made to run out on the
+    host's terms: the left-factor stage alone, waiting for completion counters that stay at zero."""
+    from monarch_attention_b200 import _cabi
+    from monarch_attention_b200.monarch_attention import make_problem
+    lib = _cabi.load()
+    case = CASES_BY_NAME["cfg3_n16384_unit_bf16"]
+    q, k, v, _ = make_inputs(case)
+    dev = torch.device("cuda:0")
+    q, k, v = q.to(dev), k.to(dev), v.to(dev)
+    good = _run(ma, case, "b200-tcgen05", q, k, v, None)
+    stream = torch.cuda.current_stream().cuda_stream
+    out = torch.empty_like(v)
+    prob = make_problem(q, k, v, out, None, case["T"], case["B"], False, _cabi.KERNEL_TCGEN05)
+    ws = torch.zeros(lib.ma_b200_workspace_bytes(C.byref(prob)), dtype=torch.uint8, device=dev)
+    assert lib.ma_b200_poll_device_status(0) == _cabi.OK
+    _cabi.raise_for_status(lib.ma_b200_selftest_wait_expiry(C.byref(prob), ws.data_ptr(), ws.numel(), stream))
+    torch.cuda.synchronize()   # returns: the kernel gave up by itself
+    assert lib.ma_b200_device_status(ws.data_ptr(), stream) == _cabi.DEVICE_WAIT_EXPIRED
+    with pytest.raises(RuntimeError, match="gave up"):
+        _run(ma, case, "b200-tcgen05", q, k, v, None)      # the next call reports it (and clears it)
+    assert lib.ma_b200_poll_device_status(0) == _cabi.OK
+    again = _run(ma, case, "b200-tcgen05", q, k, v, None)   # and the one after is an ordinary call
+    assert torch.equal(again, good)
+
+
+def test_requires_grad_inputs_are_refused(ma):
+    dev = torch.device("cuda:0")
+    q = torch.randn(1, 2, 32, 16, device=dev, requires_grad=True)
+    mod = ma.MonarchAttention(8, 2, "post")
+    with pytest.raises(RuntimeError, match="forward-only"):
+        mod(q, q, q)
+    with torch.no_grad():
+        assert mod(q, q, q).shape == q.shape
 
 
 # ---- full benchmark size: properties that need no CPU oracle run ---------------------------
@@ -284,7 +343,7 @@ def test_full_size_paths_agree_and_heads_permute(ma, full_inputs):
     a = mod_tc(q, k, v)
     b = mod_gen(q, k, v)
     check_close(a.double().cpu().numpy(), b.double().cpu().numpy(), "bf16", "tcgen05 vs generic, full size")
-    for other in ("b200-tcgen05-staged", "b200-tcgen05-tile"):
+    for other in ("b200-tcgen05-staged",):
         c = ma.MonarchAttention(128, 2, "post", impl=other)(q, k, v)
         check_close(c.double().cpu().numpy(), a.double().cpu().numpy(), "bf16", f"{other} vs fused, full size")
     for _ in range(3):   # the fused schedule must be deterministic run to run

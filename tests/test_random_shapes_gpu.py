@@ -1,5 +1,5 @@
 """Seeded random shapes: the warp-level tensor-core kernels (and the one-CTA-per-head kernel where it
-applies) against the generic kernels, which the other tests pin to the oracle and the reference.
+applies) against the CPU oracle and against the generic kernels.
 Covers what a fixed case list does not: every tile-size template, ragged last blocks, block sizes and
 counts on both sides of 16 / 32 / 64 / 128, masks that empty whole key blocks, both padding sides."""
 import random
@@ -66,7 +66,12 @@ def test_warp_level_kernels_agree_with_generic_kernels(seed):
     diff = (out - ref).abs()
     assert (diff > tol * scale).float().mean().item() <= 1e-5, what
     assert diff.max().item() <= 4 * tol * scale, what
-    assert (diff.norm() / ref.norm().clamp_min(1e-30)).item() <= 1.5e-2, what
+    assert (diff.norm() / ref.norm().clamp_min(1e-30)).item() <= 1e-2, what
+    # and against the CPU oracle itself (relative Frobenius: the tolerance of the fixed parity cases)
+    from oracle.monarch_oracle import monarch_attention_oracle
+    want = monarch_attention_oracle(q.cpu(), k.cpu(), v.cpu(), mask, T, B, c["pre"]).float()
+    fro = ((out.cpu() - want).norm() / want.norm().clamp_min(1e-30)).item()
+    assert fro <= (1e-2 if c["dt"] == torch.bfloat16 else 4e-3), f"{what}: vs oracle {fro:.3e}"
     M = -(-N // B)
     if T == 1 and B <= 32 and M <= 32 and D <= 64:
         try:

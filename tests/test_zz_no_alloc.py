@@ -5,7 +5,9 @@ a plug-in barred from the CUDA allocator, a latency-critical loop) cannot hand o
 workspace.  ``ma_b200_forward_static_scratch`` keeps the stage-to-stage state in a fixed
 array inside the library instead.  This test calls it through the C ABI twice in a row -
 the second call finds the first call's leftovers in the shared array - and checks both
-results against the ordinary entry point on the same inputs.  The file name sorts last so
+results against the ordinary entry point on the same inputs (the generic kernels with a caller-owned
+workspace, which tests/test_parity_gpu.py pins to the oracle and the reference's golden outputs on
+these very cases).  The file name sorts last so
 that a run stopping at the first failure has already exercised everything else.
 """
 import ctypes as C
