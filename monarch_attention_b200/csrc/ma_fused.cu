@@ -9,10 +9,12 @@
 // that order.  A stage-s item of a head may start once all items of stage s-1 of that head are
 // done; completion is counted in global memory (one counter per head and stage).  Because the
 // heads of a group are interleaved, the items a stage depends on were issued (G-1)*tiles items
-// earlier, so the bounded wait in the producer rarely spins.  The stage-to-stage state (ar, cr, al,
+// earlier, so the bounded wait in the planner rarely spins.  The stage-to-stage state (ar, cr, al,
 // cl, y) of a head lives in one of G state slots; the next group reuses the slots (its first stage
-// waits for the last stage of the head that had the slot), so only G heads of state are ever live,
-// they stay in L2, and lines are overwritten there instead of being written back to HBM.
+// waits for the last stage of the head that had the slot).  Every state tile is written once and read
+// once; its reader drops the tile's lines from L2 (discard.global.L2), so the state is never written
+// back to HBM, and q, k, v tiles are prefetched into L2 a few items ahead and marked evict-first on
+// their last use: HBM sees q, k, v once and the result once.
 // The launch is cooperative so that every CTA of the grid is resident, which the in-order
 // item schedule needs for forward progress.
 //
@@ -30,14 +32,19 @@
 //              P^T, goes through shared memory: P as a 16-bit value plus a 16-bit remainder, so that
 //              the column sums come out of the tensor core in fp32 precision.
 //   warps 8-11 epilogue group: waits for O, rounds it and stores rows to global memory with 32-byte
-//              stores
-//   warp 12    TMA producer: waits for the item's dependency, loads the 2-3 operand tiles and the
-//              512-byte row vector (cr or cl) of the item into a ring of thirteen 16 KB tiles
-//   warp 13    MMA issuer 1: S = A B^T for item n (tcgen05.mma, fp32 accumulator S[n%3] in tensor memory)
+//              stores and drops the state tiles the item read from L2
+//   warp 12    planner: works out the item schedule, waits for each item's dependency, keeps the
+//              accounts of the operand ring (thirteen 16 KB tiles) and leaves a descriptor per item
+//   warp 15    issuer: issues the item's TMA loads (2-3 operand tiles and the 512-byte row vector cr
+//              or cl); each of these instructions blocks for as long as the TMA unit is busy, which is
+//              why nothing else is in this warp
+//   warp 13    MMA issuer 1: S = A B^T for item n (tcgen05.mma, fp32 accumulator S[n%3] in tensor memory);
+//              its second thread is the publisher: device-scope fence and one increment of the
+//              item's (head, stage) completion counter
 //   warp 14    MMA issuer 2: the second contraction of item n into O
-//   warp 15    publisher: device-scope fence and one increment of the item's completion counter
 // All hand-offs are mbarriers; every wait is bounded and abortable (see ma_sm100.cuh).
 #include <cuda.h>
+#include <stdlib.h>
 
 #include <mutex>
 #include <type_traits>
@@ -50,15 +57,20 @@ namespace ma {
 namespace {
 
 using namespace sm100;
+#ifdef MA_EXP_NOMMA
+#define mma_f16_lo(...) ((void)0)
+#define mma_f16_ts(...) ((void)0)
+#endif
 
 constexpr int kTile = 128;
 constexpr int kHead = 64;
 constexpr uint32_t kTileBytes = kTile * kHead * 2;  // 16 KB
 
 constexpr int kEpilogueWarp0 = 8;   // warps 8..11
-constexpr int kProducerWarp = 12;
+constexpr int kPlannerWarp = 12;
 constexpr int kMma1Warp = 13;
 constexpr int kMma2Warp = 14;
+constexpr int kIssuerWarp = 15;
 constexpr int kThreads = 16 * 32;
 
 // Operand tiles live in a ring of thirteen 16 KB tiles.  An item takes two consecutive tiles (A, B) or
@@ -80,7 +92,7 @@ constexpr uint32_t kOffVec = kOffOnes + 4096;                     // kSlots x 51
 constexpr uint32_t kOffStats = kOffVec + kSlots * 512;            // 4 x 128 floats (cl of the item's rows)
 constexpr uint32_t kOffBar = kOffStats + 4 * 128 * 4;
 constexpr int kNumBarsConst = 48;
-constexpr int kDescRing = 16;  // item descriptors; deeper than the producer can run ahead (kSlots)
+constexpr int kDescRing = 16;  // item descriptors; deeper than the planner can run ahead (kSlots)
 constexpr uint32_t kOffDesc = kOffBar + 8 * kNumBarsConst + 16;
 constexpr uint32_t kSmemUsed = kOffDesc + 16 * kDescRing;
 constexpr uint32_t kSmemBytes = kSmemUsed + 1024;
@@ -91,96 +103,51 @@ static_assert(kSmemBytes <= 232448, "shared memory per CTA");
 enum {
   kBarInFull = 0,     // [8] operand tiles of an item filled by TMA
   kBarInEmpty = 8,    // [8] operand tiles of an item released by the second contraction
-  kBarSFull = 16,     // [3] S accumulator ready
-  kBarSEmpty = 19,    // [3] S / P released by the second contraction
-  kBarPFull = 22,     // [3] P written (tensor memory, or shared memory in the left-factor stage)
-  kBarOFull = 25,     // [1] O accumulator ready
-  kBarOEmpty = 26,    // [1] O accumulator read by the epilogue group
-  kBarDone = 28,      // [4] item stored to global memory by all 128 epilogue threads
-  kBarPubFree = 32,   // [4] completion of that item published
+  kBarPlan = 16,      // [8] descriptor of an item written by the planner
+  kBarSFull = 24,     // [3] S accumulator ready
+  kBarSEmpty = 27,    // [3] S / P released by the second contraction
+  kBarPFull = 30,     // [3] P written (tensor memory, or shared memory in the left-factor stage)
+  kBarOFull = 33,     // [1] O accumulator ready
+  kBarOEmpty = 34,    // [1] O accumulator read by the epilogue group
   kBarStat = 36,      // [4] row statistics of the item written by its softmax group
-  kNumBars = 40
+  kBarDone = 40,      // [4] item stored to global memory by all 128 epilogue threads
+  kBarPubFree = 44,   // [4] completion of that item published
+  kNumBars = 48
 };
 static_assert(kNumBars <= kNumBarsConst, "barrier count");
+constexpr int kEpilogueBarrier = 1;  // named barriers of the 128 epilogue threads: this one and the next
 
 struct FusedArgs {
   int stage_begin, stage_end;  // stages [begin, end) of the 2T stages run in this launch
   int group;                   // heads interleaved per group
   int wait_deps;               // wait on the completion counters of the previous stage
   int reuse_slots;             // state of head (group g, position p) lives in slot p (needs wait_deps)
-  int spin_limit;              // iterations of the producer's dependency wait before it gives up
+  int spin_limit;              // iterations of the planner's dependency wait before it gives up
   int* counters;               // (E*H, 2T) ints, zeroed before the first launch of a call
   int* host_status;            // mapped host word that receives the code of a wait that gave up, or nullptr
+#ifdef MA_TRACE
+  long long* trace;            // [2 CTAs][64 items][16 events] clock64 stamps
+#endif
 };
 
 struct Item {
-  int kind, first, stage, eh, tile, hs;  // hs: state slot of the head
-};
-
-// Walks the items of one CTA (global indices blockIdx.x, blockIdx.x + grid, ...) without a division
-// per item: the position (group, stage, head in group, tile) is carried along.
-struct ItemCursor {
-  int gi, sl, hh, tile, gh;  // group, stage within the launch, head within the group, tile, heads in this group
-  int idx, total, stride, nst, group, EH, stage_begin, last_stage, reuse;
-  int tph;  // tiles per head and stage: N / 128
-
-  __device__ __forceinline__ void init(int first_idx, int stride_, const Geometry& g, const FusedArgs& a) {
-    EH = g.E * g.H;
-    nst = a.stage_end - a.stage_begin;
-    group = a.group;
-    reuse = a.reuse_slots;
-    stage_begin = a.stage_begin;
-    last_stage = 2 * g.T - 1;
-    tph = g.N / kTile;
-    total = nst * tph * EH;
-    stride = stride_;
-    idx = first_idx;
-    const int per_group = nst * group * tph;
-    gi = idx / per_group;
-    int r = idx - gi * per_group;
-    gh = min(group, EH - gi * group);
-    if (gh < 1) gh = 1;
-    sl = r / (gh * tph);
-    r -= sl * gh * tph;
-    hh = r / tph;
-    tile = r - hh * tph;
-  }
-  __device__ __forceinline__ bool valid() const { return idx < total; }
-  __device__ __forceinline__ void next() {
-    idx += stride;
-    tile += stride;
-    while (tile >= tph) {
-      tile -= tph;
-      if (++hh == gh) {
-        hh = 0;
-        if (++sl == nst) {
-          sl = 0;
-          ++gi;
-          gh = min(group, EH - gi * group);
-          if (gh < 1) gh = 1;
-        }
-      }
-    }
-  }
-  __device__ __forceinline__ Item get() const {
-    Item it;
-    it.tile = tile;
-    it.eh = gi * group + hh;
-    it.hs = reuse ? hh : it.eh;
-    it.stage = stage_begin + sl;
-    it.kind = it.stage == last_stage
-                  ? kStageOutput
-                  : (it.stage == last_stage - 1 ? kStageRightWithV : ((it.stage & 1) ? kStageLeft : kStageRight));
-    it.first = it.stage == 0;
-    return it;
-  }
+  int kind, first, stage, eh, tile, hs, e, h, t0, p_dist;  // hs: state slot of the head; t0: first ring tile
 };
 
 // Round an fp32 pair through the 16-bit storage type (the reference rounds every contraction result to
 // the storage type before the fp32 softmax arithmetic, ma/ma_torch.py:11, :27, :56).
+// Done on the FMA pipe (Veltkamp split with the constant 2^(24-p) + 1 for a p-bit significand: the high
+// part is x rounded to nearest at p bits), because the conversion instructions share a pipe with the
+// exponentials, which is the busiest one of this kernel.
 template <typename T>
 __device__ __forceinline__ float2 round2(float2 x) {
-  return unpack2<T>(pack2<T>(x.x, x.y));
+  constexpr float c = std::is_same<T, __nv_bfloat16>::value ? 65537.0f : 8193.0f;
+  const float2 big = mul2(x, make_float2(c, c));
+  return add2(big, sub2(x, big));
+}
+
+__device__ __forceinline__ void red_release_add(int* p, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 template <typename T, int PER>  // PER: key blocks (or columns j) per 128-row tile: 1 (block size 128) or 2 (64)
@@ -195,6 +162,12 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + kOffBar + 8 * kNumBarsConst + 8);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef MA_TRACE
+  const int tr_cta = blockIdx.x == 0 ? 0 : (blockIdx.x == 77 ? 1 : -1);
+#define TR(n_, ev_) do { if (tr_cta >= 0 && args.trace != nullptr && (n_) < 64) args.trace[(tr_cta * 64 + (n_)) * 16 + (ev_)] = clock64(); } while (0)
+#else
+#define TR(n_, ev_) do { } while (0)
+#endif
   constexpr int kFmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
   const int tph = g.N / kTile;  // tiles per head and stage
   constexpr int per = PER;
@@ -204,7 +177,11 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
   const int nst_all = 2 * g.T;
 
   if (tid == 0) {
-    for (int i = 0; i < kSlots; ++i) { mbar_init(bar(kBarInFull + i), 1); mbar_init(bar(kBarInEmpty + i), 1); }
+    for (int i = 0; i < kSlots; ++i) {
+      mbar_init(bar(kBarInFull + i), 1);
+      mbar_init(bar(kBarInEmpty + i), 1);
+      mbar_init(bar(kBarPlan + i), 1);
+    }
     for (int i = 0; i < kSBuffers; ++i) {
       mbar_init(bar(kBarSFull + i), 1);
       mbar_init(bar(kBarSEmpty + i), 1);
@@ -213,8 +190,8 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
     mbar_init(bar(kBarOFull), 1);
     mbar_init(bar(kBarOEmpty), 128);
     for (int i = 0; i < 4; ++i) {
-      mbar_init(bar(kBarDone + i), 128);
       mbar_init(bar(kBarStat + i), 128);
+      mbar_init(bar(kBarDone + i), 128);
       mbar_init(bar(kBarPubFree + i), 1);
     }
     *abort_flag = 0;
@@ -238,21 +215,24 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  // Only the producer walks the item schedule.  It leaves a four-word descriptor per item in a small
-  // ring (written before the arrive that opens the item's operand barrier, so every later hand-off
-  // carries it); the other roles read it once their first wait for the item has returned.
+  // Only the planner walks the item schedule.  It leaves a four-word descriptor per item in a small
+  // ring (written before the arrive that hands the item to the issuer, whose arrive on the item's
+  // operand barrier carries it on to every later hand-off); the other roles read it once their first
+  // wait for the item has returned.
   const int n_items = total > (int)blockIdx.x ? (total - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-  auto read_item = [&](int n, int* first_tile, int* p_dist) {
+  auto read_item = [&](int n) {
     const int4 d = *reinterpret_cast<const int4*>(base_ptr + kOffDesc + (n & (kDescRing - 1)) * 16);
     Item it;
     it.kind = d.x & 3;
     it.first = (d.x >> 2) & 1;
-    *first_tile = (d.x >> 3) & 15;
+    it.t0 = (d.x >> 3) & 15;
     it.tile = (d.x >> 8) & 255;
-    it.stage = d.x >> 16;
+    it.stage = (d.x >> 16) & 4095;
+    it.p_dist = (d.x >> 28) & 7;
     it.eh = d.y;
     it.hs = d.z;
-    *p_dist = d.w;
+    it.e = (int)((unsigned)d.w >> 16);
+    it.h = d.w & 0xffff;
     return it;
   };
   auto give_up = [&](int code) {
@@ -268,115 +248,168 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
   // 256 x 192 + 128 x 80 + 128 x 48 = 65536 = 512 x 128, so the increase can always be granted.
   // (What setmaxnreg redistributes is the allocation the CTA was launched with - threads x registers
   // per thread - not the whole register file: a request beyond that pool blocks for ever.)
-  if (warp >= kProducerWarp) {
+  if (warp >= kPlannerWarp) {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
-  if (warp == kProducerWarp) {
-    // =========================== TMA producer ===========================================
-    if (lane == 0) {
-      int n = 0, issued = 0;
-      int free_tiles = kRingTiles, oldest = 0, ring_pos = 0;  // ring accounting: items [oldest, n) hold tiles
-      int lefts = 0;                                          // left-factor items among them
-      // per in-flight item, at index m % kSlots, packed: tiles held (incl. skipped tail) | left-factor item << 8 |
-      // holds a tile of the P region << 9
-      int held[kSlots];
-#pragma unroll
-      for (int i = 0; i < kSlots; ++i) held[i] = 0;
-      auto held_at = [&](int m) {
-        int v = 0;
-#pragma unroll
-        for (int i = 0; i < kSlots; ++i) v = (m % kSlots) == i ? held[i] : v;
-        return v;
-      };
-      auto retire_oldest = [&]() {
-        const int v = held_at(oldest);
-        free_tiles += v & 255;
-        lefts -= (v >> 8) & 1;
-        ++oldest;
-      };
-      ItemCursor cur;
-      bool ok = true;
-      for (cur.init(blockIdx.x, gridDim.x, g, args); cur.valid() && ok; cur.next(), ++n) {
-        const Item it = cur.get();
-        const int e = it.eh / g.H, h = it.eh - e * g.H;
-        const int slot = n % kSlots;
-        if (args.wait_deps) {
+  if (warp == kPlannerWarp) {
+    // =========================== planner =================================================
+    // The warp works in batches of kBatch items: lane L < kBatch works out item n0 + L of this CTA (the
+    // divisions of the schedule) and reads the completion counter it depends on, so that the latency of
+    // those loads is paid once per batch (a longer batch would look further ahead than dependencies are
+    // complete); lanes kBatch .. 2 kBatch - 1 do the same for the batch after it, only to bring its q, k,
+    // v tiles into L2 ahead of time.  Then lane 0 takes the items one by one: ring accounts, descriptor,
+    // hand-off to the issuer.
+    constexpr int kBatch = 4;
+    int free_tiles = kRingTiles, oldest = 0, ring_pos = 0;  // ring accounting (lane 0): items [oldest, n) hold tiles
+    int lefts = 0;                                          // left-factor items among them
+    int last_p = -1;  // newest item that is a left-factor item or holds a tile of the P region
+    // per in-flight item m, six bits at 6*(m % kSlots): tiles held (incl. skipped tail, <= 15) | left-factor item << 4
+    unsigned long long held = 0ull;
+    bool ok = true;
+    const int EH = g.E * g.H, nst = args.stage_end - args.stage_begin, last_stage = nst_all - 1;
+    const int per_group = nst * args.group * tph;
+    for (int n0 = 0; n0 < n_items && ok; n0 += kBatch) {
+      const int my_n = n0 + lane;
+      const int idx = (int)blockIdx.x + my_n * (int)gridDim.x;
+      int w0 = 0, my_eh = 0, my_hs = 0, my_eh_hi = 0, dep_ok = 1;
+      int pf_kind = -1, pf_tile = 0;
+      if (lane < 2 * kBatch && my_n < n_items) {
+        const int gi = idx / per_group;
+        int r = idx - gi * per_group;
+        int gh = min(args.group, EH - gi * args.group);
+        if (gh < 1) gh = 1;
+        const int sl = r / (gh * tph);
+        r -= sl * gh * tph;
+        const int hh = r / tph, tile = r - hh * tph;
+        my_eh = gi * args.group + hh;
+        my_hs = args.reuse_slots ? hh : my_eh;
+        const int stage = args.stage_begin + sl;
+        const int kind = stage == last_stage
+                             ? kStageOutput
+                             : (stage == last_stage - 1 ? kStageRightWithV : ((stage & 1) ? kStageLeft : kStageRight));
+        w0 = kind | ((stage == 0 ? 1 : 0) << 2) | (tile << 8) | (stage << 16);
+        const int e = my_eh / g.H;
+        my_eh_hi = (e << 16) | (my_eh - e * g.H);  // (batch element, head) of the user tensors
+        if (lane >= kBatch || n0 == 0) { pf_kind = kind; pf_tile = tile; }
+        if (args.wait_deps && lane < kBatch) {
           const int* ctr = nullptr;
-          if (it.stage > 0) ctr = args.counters + it.eh * nst_all + (it.stage - 1);
-          else if (args.reuse_slots && cur.gi > 0) ctr = args.counters + (it.eh - args.group) * nst_all + (nst_all - 1);
-          if (ctr != nullptr) {
+          if (stage > 0) ctr = args.counters + my_eh * nst_all + (stage - 1);
+          else if (args.reuse_slots && gi > 0) ctr = args.counters + (my_eh - args.group) * nst_all + (nst_all - 1);
+          if (ctr != nullptr) dep_ok = ld_acquire_gpu(ctr) >= tph ? 1 : 0;
+        }
+      }
+      if (pf_kind >= 0) {
+        const int e = (int)((unsigned)my_eh_hi >> 16), h = my_eh_hi & 0xffff;
+        if (pf_kind == kStageRight || pf_kind == kStageRightWithV) {
+          if (w0 & 4) tma_prefetch_5d(&maps.q_blk, 0, 0, pf_tile, h, e);
+          tma_prefetch_5d(&maps.k_blk, 0, 0, pf_tile, h, e);
+          if (pf_kind == kStageRightWithV) tma_prefetch_5d(&maps.v_blk, 0, 0, pf_tile, h, e);
+        } else {
+          for (int jj = 0; jj < per; ++jj) tma_prefetch_5d(&maps.q_col, 0, pf_tile * per + jj, 0, h, e);
+        }
+      }
+      __syncwarp();
+      const int batch = min(kBatch, n_items - n0);
+      for (int i = 0; i < batch && ok; ++i) {
+        const int n = n0 + i, slot = n % kSlots;
+        const int d0 = __shfl_sync(0xffffffffu, w0, i), eh = __shfl_sync(0xffffffffu, my_eh, i);
+        const int hs = __shfl_sync(0xffffffffu, my_hs, i), ehh = __shfl_sync(0xffffffffu, my_eh_hi, i);
+        const int dok = __shfl_sync(0xffffffffu, dep_ok, i);
+        if (lane == 0) {
+          const int kind = d0 & 3, stage = d0 >> 16;
+          const bool left = kind == kStageLeft;
+          const int ntiles = (kind == kStageRightWithV || kind == kStageOutput) ? 3 : 2;
+          TR(n, 0);
+          if (!dok) {  // not yet complete when the batch was prepared: wait here
+            const int* ctr = stage > 0 ? args.counters + eh * nst_all + (stage - 1)
+                                       : args.counters + (eh - args.group) * nst_all + (nst_all - 1);
             bool ready = false;
             for (int spin = 0; spin < args.spin_limit; ++spin) {
               if (ld_acquire_gpu(ctr) >= tph) { ready = true; break; }
               if ((spin & 255) == 255 && *abort_flag) break;
               __nanosleep(32);
             }
-            if (!ready) { give_up(201); break; }
-            fence_proxy_async_all();  // the state was written with ordinary stores; the loads below are TMA
+            if (!ready) { give_up(201); ok = false; }
+          }
+          int t0 = 0, charged = 0;
+          while (ok) {
+            const int limit = (left || lefts > 0) ? kRingLeft : kRingTiles;
+            int pos = ring_pos, sk = 0;
+            if (pos + ntiles > limit) { sk = kRingTiles - pos; pos = 0; }
+            if (free_tiles >= ntiles + sk && n - oldest < kSlots) { t0 = pos; charged = ntiles + sk; break; }
+            // items whose second contraction has completed give their tiles back (in order)
+            if (!mbar_wait_abortable(bar(kBarInEmpty + oldest % kSlots), (uint32_t)(oldest / kSlots) & 1u, abort_flag)) {
+              give_up(202);
+              ok = false;
+              break;
+            }
+            const int v = (int)(held >> (6 * (oldest % kSlots))) & 63;
+            free_tiles += v & 15;
+            lefts -= (v >> 4) & 1;
+            ++oldest;
+          }
+          if (ok) {
+            TR(n, 1);
+            // A left-factor item writes P into the P region: it has to wait for the newest older item that
+            // is a left-factor item itself or holds one of those tiles (items complete in order).
+            const int p_dist = (left && last_p >= oldest) ? n - last_p : 0;
+            ring_pos = t0 + ntiles;
+            if (left || ring_pos > kRingLeft || charged > ntiles) last_p = n;
+            if (ring_pos == kRingTiles) ring_pos = 0;
+            held = (held & ~(63ull << (6 * slot))) | ((unsigned long long)(charged | ((left ? 1 : 0) << 4)) << (6 * slot));
+            free_tiles -= charged;
+            lefts += left ? 1 : 0;
+            *reinterpret_cast<int4*>(base_ptr + kOffDesc + (n & (kDescRing - 1)) * 16) =
+                make_int4((d0 & 0x0fffff07) | (t0 << 3) | (p_dist << 28), eh, hs, ehh);
+            mbar_arrive(bar(kBarPlan + slot));
           }
         }
-        // items whose second contraction has completed give their tiles back (in order)
-        while (oldest < n && mbar_test(bar(kBarInEmpty + oldest % kSlots), (uint32_t)(oldest / kSlots) & 1u))
-          retire_oldest();
-        const bool left = it.kind == kStageLeft;
-        const int ntiles = (it.kind == kStageRightWithV || it.kind == kStageOutput) ? 3 : 2;
-        int t0 = 0, charged = 0;
-        for (;;) {
-          const int limit = (left || lefts > 0) ? kRingLeft : kRingTiles;
-          int pos = ring_pos, sk = 0;
-          if (pos + ntiles > limit) { sk = kRingTiles - pos; pos = 0; }
-          if (free_tiles >= ntiles + sk && n - oldest < kSlots) { t0 = pos; charged = ntiles + sk; break; }
-          if (!mbar_wait_abortable(bar(kBarInEmpty + oldest % kSlots), (uint32_t)(oldest / kSlots) & 1u, abort_flag)) {
-            give_up(202);
-            ok = false;
-            break;
-          }
-          retire_oldest();
-        }
-        if (!ok) break;
-        // A left-factor item writes P into the P region: it has to wait for the newest older item that
-        // is a left-factor item itself or holds one of those tiles (items complete in order).
-        int p_dist = 0;
-        if (left) {
-          for (int m = oldest; m < n; ++m)
-            if (held_at(m) >> 8) p_dist = n - m;
-        }
-        ring_pos = t0 + ntiles;
-        const int uses_p = (ring_pos > kRingLeft || charged > ntiles) ? 1 : 0;
-        if (ring_pos == kRingTiles) ring_pos = 0;
-        {
-          const int v = charged | ((left ? 1 : 0) << 8) | (uses_p << 9);
-#pragma unroll
-          for (int i = 0; i < kSlots; ++i)
-            if (slot == i) held[i] = v;
-        }
-        free_tiles -= charged;
-        lefts += left ? 1 : 0;
-        const uint32_t sA = base + kOffSlots + t0 * kTileBytes, sB = sA + kTileBytes, sV = sB + kTileBytes;
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      }
+    }
+  } else if (warp == kIssuerWarp) {
+    // =========================== issuer: TMA loads ========================================
+    if (lane == 0) {
+      const unsigned long long pol_first = l2_policy_evict_first();
+      int issued = 0;
+      for (int n = 0; n < n_items; ++n) {
+        const int slot = n % kSlots;
+        if (!mbar_wait_abortable(bar(kBarPlan + slot), (uint32_t)(n / kSlots) & 1u, abort_flag)) break;  // the planner gave up
+        const Item it = read_item(n);
+        const bool right = it.kind == kStageRight || it.kind == kStageRightWithV;
+        const bool three = it.kind == kStageRightWithV || it.kind == kStageOutput;
+        const bool has_vec = !(right && it.first);
+        const uint32_t sA = base + kOffSlots + it.t0 * kTileBytes, sB = sA + kTileBytes, sV = sB + kTileBytes;
         const uint32_t vec = base + kOffVec + slot * 512;
         const uint32_t full = bar(kBarInFull + slot);
-        const bool right = it.kind == kStageRight || it.kind == kStageRightWithV;
-        const bool three = ntiles == 3;
-        const bool has_vec = !(right && it.first);
-        *reinterpret_cast<int4*>(base_ptr + kOffDesc + (n & (kDescRing - 1)) * 16) =
-            make_int4(it.kind | (it.first << 2) | (t0 << 3) | (it.tile << 8) | (it.stage << 16), it.eh, it.hs, p_dist);
         mbar_expect_tx(full, (three ? 3u : 2u) * kTileBytes + (has_vec ? 512u : 0u));
+        issued = n + 1;
+        // q, k, v tiles that no later stage reads again are marked to leave L2 first
         if (right) {
-          if (it.first) tma_load_5d(sA, &maps.q_blk, full, 0, 0, it.tile, h, e);
+          if (it.first) tma_load_5d(sA, &maps.q_blk, full, 0, 0, it.tile, it.h, it.e);
           else tma_load_5d(sA, &maps.ar_blk, full, 0, 0, it.tile, it.hs, 0);
-          tma_load_5d(sB, &maps.k_blk, full, 0, 0, it.tile, h, e);
-          if (three) tma_load_5d(sV, &maps.v_blk, full, 0, 0, it.tile, h, e);
+          if (three) {
+            tma_load_5d_hint(sB, &maps.k_blk, full, 0, 0, it.tile, it.h, it.e, pol_first);
+            tma_load_5d_hint(sV, &maps.v_blk, full, 0, 0, it.tile, it.h, it.e, pol_first);
+          } else {
+            tma_load_5d(sB, &maps.k_blk, full, 0, 0, it.tile, it.h, it.e);
+          }
           if (has_vec) bulk_load(vec, g.cr + ((long long)it.hs * g.M + it.tile * per) * g.B, 512, full);
         } else {
           // one box per column j of the tile: rows jj*(128/per) + l, the same row order as the blocks of
           // a right-factor tile (a row's own columns are then the same for every lane of a warp, which
           // the warp-wide tensor-memory loads of the softmax need)
-          for (int jj = 0; jj < per; ++jj)
-            tma_load_5d(sA + jj * (kTileBytes / per), &maps.q_col, full, 0, it.tile * per + jj, 0, h, e);
+          for (int jj = 0; jj < per; ++jj) {
+            if (three) tma_load_5d_hint(sA + jj * (kTileBytes / per), &maps.q_col, full, 0, it.tile * per + jj, 0, it.h, it.e, pol_first);
+            else tma_load_5d(sA + jj * (kTileBytes / per), &maps.q_col, full, 0, it.tile * per + jj, 0, it.h, it.e);
+          }
           tma_load_5d(sB, &maps.al_blk, full, 0, 0, it.tile, it.hs, 0);
           if (three) tma_load_5d(sV, &maps.y_blk, full, 0, 0, it.tile, it.hs, 0);
           bulk_load(vec, g.cl + ((long long)it.hs * g.B + it.tile * per) * g.M, 512, full);
         }
-        issued = n + 1;
+        TR(n, 2);
+#ifdef MA_TRACE
+        if (tr_cta >= 0 && args.trace != nullptr && n < 64) args.trace[(tr_cta * 64 + n) * 16 + 15] = it.stage * 1000 + it.eh;
+#endif
       }
       // Drain: make sure every copy this thread started has landed before the CTA may exit.
       for (int m = max(0, issued - kSlots); m < issued; ++m)
@@ -395,8 +428,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       for (int n = 0; n < n_items; ++n) {
         const int slot = n % kSlots, sb = n % kSBuffers;
         if (!mbar_wait_abortable(bar(kBarInFull + slot), (uint32_t)(n / kSlots) & 1u, abort_flag)) { give_up(301); break; }
-        int t0, pd;
-        (void)read_item(n, &t0, &pd);
+        const int t0 = read_item(n).t0;
         if (!mbar_wait_abortable(bar(kBarSEmpty + sb), ((uint32_t)(n / kSBuffers) & 1u) ^ 1u, abort_flag)) { give_up(302); break; }
         tc_fence_after();
         const uint32_t dA = dA0 + t0 * kTileStep, dB = dA + kTileStep;
@@ -404,8 +436,23 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         for (int kk = 0; kk < kHead / 16; ++kk) mma_f16_lo(tmem + sb * 128, dA + kk * 2, dB + kk * 2, idesc1, kk > 0);
         mma_commit(bar(kBarSFull + sb));
       }
+    } else if (lane == 1 && args.wait_deps) {
+      // =========================== publisher (second thread of this warp) ====================
+      // Makes the stores of every finished item visible device-wide and counts the item in its (head,
+      // stage) completion counter.  The fence waits for the group's stores to be acknowledged, which
+      // takes about a microsecond: a thread of its own keeps that off the epilogue group's path.  (The
+      // output stage is consumed only when state slots are reused, by the next head in the slot.)
+      for (int n = 0; n < n_items; ++n) {
+        if (!mbar_wait_abortable(bar(kBarDone + (n & 3)), (uint32_t)(n >> 2) & 1u, abort_flag)) { give_up(601); break; }
+        const Item it = read_item(n);
+        if (it.stage != nst_all - 1 || args.reuse_slots) {
+          __threadfence();
+          atomicAdd(args.counters + it.eh * nst_all + it.stage, 1);
+        }
+        mbar_arrive(bar(kBarPubFree + (n & 3)));
+      }
     }
-  } else if (warp == kMma2Warp) {
+  } else {
     // =========================== MMA issuer 2: O = P [B | V] =================================
     if (lane == 0) {
       const uint32_t dP_mn0 = smem_desc_lo(base + kOffPreg, kTileBytes);   // P^T as MN-major A operand (left stage)
@@ -415,12 +462,13 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       for (int n = 0; n < n_items; ++n) {
         const int sb = n % kSBuffers, slot = n % kSlots;
         if (!mbar_wait_abortable(bar(kBarPFull + sb), (uint32_t)(n / kSBuffers) & 1u, abort_flag)) { give_up(303); break; }
-        int t0, pd;
-        const int kind = read_item(n, &t0, &pd).kind;
+        TR(n, 10);
+        const Item it = read_item(n);
+        const int kind = it.kind;
         if (!mbar_wait_abortable(bar(kBarOEmpty), ((uint32_t)n & 1u) ^ 1u, abort_flag)) { give_up(304); break; }
         tc_fence_after();
         // tiles of the item: A, B, V
-        const uint32_t dA = dTmn0 + t0 * kTileStep, dB = dA + kTileStep, dV = dB + kTileStep;
+        const uint32_t dA = dTmn0 + it.t0 * kTileStep, dB = dA + kTileStep, dV = dB + kTileStep;
         const uint32_t tmem_o = tmem + kTmemO, tmem_p = tmem + sb * 128;
         if (kind == kStageRight) {
           constexpr uint32_t idesc = instr_desc(kFmt, 0, 1, kHead, kTile);
@@ -451,23 +499,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         mma_commit(bar(kBarOFull));
         mma_commit(bar(kBarSEmpty + sb));
         mma_commit(bar(kBarInEmpty + slot));
-      }
-    }
-  } else {
-    // =========================== publisher =====================================================
-    // Makes the stores of every finished item visible device-wide and counts the item in its
-    // (head, stage) completion counter, off the critical path of the epilogue group.
-    if (lane == 0 && args.wait_deps) {
-      for (int n = 0; n < n_items; ++n) {
-        if (!mbar_wait_abortable(bar(kBarDone + (n & 3)), (uint32_t)(n >> 2) & 1u, abort_flag)) { give_up(601); break; }
-        int t0, pd;
-        const Item it = read_item(n, &t0, &pd);
-        // the output stage is consumed only when state slots are reused (by the next head in the slot)
-        if (it.stage != nst_all - 1 || args.reuse_slots) {
-          __threadfence();
-          atomicAdd(args.counters + it.eh * nst_all + it.stage, 1);
-        }
-        mbar_arrive(bar(kBarPubFree + (n & 3)));
+        TR(n, 12);
       }
     }
   }
@@ -476,15 +508,19 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
     // =========================== epilogue group =================================================
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const unsigned long long pol_first = l2_policy_evict_first();
     for (int n = 0; n < n_items; ++n) {
-      if (!mbar_wait_abortable(bar(kBarStat + (n & 3)), (uint32_t)(n >> 2) & 1u, abort_flag) ||
-          !mbar_wait_abortable(bar(kBarOFull), (uint32_t)n & 1u, abort_flag)) {
-        give_up(501);
+      const bool got = mbar_wait_abortable(bar(kBarStat + (n & 3)), (uint32_t)(n >> 2) & 1u, abort_flag) &&
+                       mbar_wait_abortable(bar(kBarOFull), (uint32_t)n & 1u, abort_flag);
+      // all 128 threads leave together or not at all (a thread that went on alone would strand the
+      // others at the group barrier below)
+      if (named_barrier_or(kEpilogueBarrier, 128, !got)) {
+        if (!got) give_up(501);
         break;
       }
       tc_fence_after();
-      int t0_unused, pd_unused;
-      const Item it = read_item(n, &t0_unused, &pd_unused);
+      if (tid == 256) TR(n, 13);
+      const Item it = read_item(n);
       const float stat = reinterpret_cast<const float*>(base_ptr + kOffStats)[(n & 3) * 128 + row];
       const uint32_t tmem_o = tmem + lane_base + kTmemO;
       T* dst0;
@@ -500,17 +536,18 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         dst0 = reinterpret_cast<T*>(g.al) + rr * kHead;
         g.cl[rr] = stat;
         row_y = rr;
-        scale = g.sm_scale;  // a power of two for D = 64: scaling before or after the rounding is the same
+        // sm_scale is a power of two for D = 64, so scaling before or after the rounding is the same: the
+        // plain right-factor stage has it folded into P already, the stage with V applies it here
+        if (it.kind == kStageRightWithV) scale = g.sm_scale;
       } else if (it.kind == kStageLeft) {
         dst0 = reinterpret_cast<T*>(g.ar) + (((long long)it.hs * g.M + rin) * g.B + it.tile * per + rblk) * kHead;
       } else {
-        const int e = it.eh / g.H, h = it.eh - e * g.H;
-        dst0 = reinterpret_cast<T*>(const_cast<void*>(g.out.ptr)) + (long long)e * g.out.se + (long long)h * g.out.sh +
+        dst0 = reinterpret_cast<T*>(const_cast<void*>(g.out.ptr)) + (long long)it.e * g.out.se + (long long)it.h * g.out.sh +
                ((long long)rin * g.B + it.tile * per + rblk) * g.out.sn;
       }
       // 64 accumulator columns -> one 128-byte row: both chunk loads in flight, then 4 x 32-byte stores
-      // (every touched sector is written whole)
-      auto store_row = [&](T* dst, uint32_t taddr, float sc) {
+      // (every touched sector is written whole); the result rows are not read again and leave L2 first
+      auto store_row = [&](T* dst, uint32_t taddr, float sc, bool streaming) {
         float o0[32], o1[32];
         tmem_ld32_nowait(taddr, o0);
         tmem_ld32_nowait(taddr + 32, o1);
@@ -520,29 +557,55 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         for (int h8 = 0; h8 < 4; ++h8) {
           const float* p = (h8 < 2 ? o0 : o1) + (h8 & 1) * 16;
           uint32_t w[8];
+          if (sc != 1.0f) {
+            const float2 scv = make_float2(sc, sc);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) w[i] = pack2<T>(p[2 * i] * sc, p[2 * i + 1] * sc);
-          st_global_v8(dst + h8 * 16, w);
+            for (int i = 0; i < 8; ++i) {
+              const float2 t = mul2(make_float2(p[2 * i], p[2 * i + 1]), scv);
+              w[i] = pack2<T>(t.x, t.y);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w[i] = pack2<T>(p[2 * i], p[2 * i + 1]);
+          }
+          if (streaming) st_global_v8_hint(dst + h8 * 16, w, pol_first);
+          else st_global_v8(dst + h8 * 16, w);
         }
       };
-      store_row(dst0, tmem_o, scale);
+#ifndef MA_EXP_NOEPI
+      store_row(dst0, tmem_o, scale, it.kind == kStageOutput);
       if (it.kind == kStageRightWithV) {
-        store_row(reinterpret_cast<T*>(g.y) + row_y * kHead, tmem_o + kHead, 1.0f);
+        store_row(reinterpret_cast<T*>(g.y) + row_y * kHead, tmem_o + kHead, 1.0f, false);
       } else if (it.kind == kStageLeft) {
         float o[32];
         tmem_ld32(tmem_o + kHead, o);
         g.cr[((long long)it.hs * g.M + rin) * g.B + it.tile * per + rblk] = o[0];
       }
+#endif
       tc_fence_before();
       mbar_arrive(bar(kBarOEmpty));
+      if (tid == 256) TR(n, 5);
       if (args.wait_deps) {
-        // hand the item to the publisher warp (4-deep ring)
-        if (!mbar_wait_abortable(bar(kBarPubFree + (n & 3)), ((uint32_t)(n >> 2) & 1u) ^ 1u, abort_flag)) {
-          give_up(502);
-          break;
+        // The state tiles this item read (each is written once and read once) are dead: drop their lines
+        // from L2 so that they are never written back to HBM and make room at once.  One 128-byte row per
+        // thread; a tile is 128 consecutive rows.
+        const long long trow = ((long long)it.hs * kTile * tph + (long long)it.tile * kTile + row) * kHead;
+        if (it.kind == kStageLeft || it.kind == kStageOutput) {
+          l2_discard_line(reinterpret_cast<const T*>(g.al) + trow);
+          if (it.kind == kStageOutput) l2_discard_line(reinterpret_cast<const T*>(g.y) + trow);
+        } else if (!it.first) {
+          l2_discard_line(reinterpret_cast<const T*>(g.ar) + trow);
         }
+        // The rows stored above are read by other CTAs with TMA, i.e. through the async proxy: the
+        // writer orders its generic-proxy stores before it (a fence on the reading side would make the
+        // issuer wait for its own copies in flight, which serialises the loads of consecutive items).
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        if (tid == 256) TR(n, 4);
+        // hand the item to the publisher (4-deep ring)
+        if (!mbar_wait_abortable(bar(kBarPubFree + (n & 3)), ((uint32_t)(n >> 2) & 1u) ^ 1u, abort_flag)) give_up(502);
         mbar_arrive(bar(kBarDone + (n & 3)));
       }
+      if (tid == 256) TR(n, 14);
     }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 192;");
@@ -559,13 +622,178 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       const int slot = n % kSlots, sb = n % kSBuffers;
       const float* vec = reinterpret_cast<const float*>(base_ptr + kOffVec + slot * 512) + (per > 1 ? 64 * h0 : 0);
       if (!mbar_wait_abortable(bar(kBarInFull + slot), (uint32_t)(n / kSlots) & 1u, abort_flag)) { give_up(401); break; }
-      int tile0, p_dist;
-      const Item it = read_item(n, &tile0, &p_dist);
+      const Item it = read_item(n);
       const bool right = it.kind == kStageRight || it.kind == kStageRightWithV;
       if (!mbar_wait_abortable(bar(kBarSFull + sb), (uint32_t)(n / kSBuffers) & 1u, abort_flag)) { give_up(402); break; }
       tc_fence_after();
+      if ((tid & 127) == 0) TR(n, 6);
       const uint32_t tmem_s = tmem + lane_base + sb * 128;
 
+#ifdef MA_ROLLED
+      // Three passes over the row's own columns of S, each a short loop over 32-column chunks read from
+      // tensor memory one chunk ahead of the arithmetic (two register buffers): maximum; exponentials,
+      // row sum and entropy, the exponentials written back over S as fp32; normalised factor, rounded,
+      // over the first half of S as the A operand of the second contraction.  The loops are kept rolled
+      // so that the code of all roles of the CTA stays resident in the instruction caches.
+      constexpr int kChunks = kCols / 32;
+      const uint32_t tmem_row = tmem_s + 64 * h0;
+      float ca[32], cb[32];
+      float stat = 0.f, inv;
+      float mul = kLog2e, noff;
+      // logits of a chunk up to a positive row factor:  right-factor stages round(S), others round(S) - cl[m]
+      auto logits = [&](float (&x)[32], int c) {
+        if (right) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float2 a = round2<T>(make_float2(x[i], x[i + 1]));
+            x[i] = a.x; x[i + 1] = a.y;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float4 c4 = *reinterpret_cast<const float4*>(vec + 32 * c + i);
+            const float2 a = sub2(round2<T>(make_float2(x[i], x[i + 1])), make_float2(c4.x, c4.y));
+            const float2 b2 = sub2(round2<T>(make_float2(x[i + 2], x[i + 3])), make_float2(c4.z, c4.w));
+            x[i] = a.x; x[i + 1] = a.y; x[i + 2] = b2.x; x[i + 3] = b2.y;
+          }
+        }
+      };
+      float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+      auto max_chunk = [&](float (&x)[32], int c) {
+        logits(x, c);
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          m0 = max3(m0, x[i], x[i + 1]);
+          m1 = max3(m1, x[i + 2], x[i + 3]);
+          m2 = max3(m2, x[i + 4], x[i + 5]);
+          m3 = max3(m3, x[i + 6], x[i + 7]);
+        }
+      };
+      tmem_ld32_nowait(tmem_row, ca);
+#pragma unroll 1
+      for (int c = 0; c < kChunks; c += 2) {
+        tmem_wait_ld(ca); tmem_ld32_nowait(tmem_row + 32 * (c + 1), cb); max_chunk(ca, c);
+        tmem_wait_ld(cb); tmem_ld32_nowait(tmem_row + 32 * (c + 2 < kChunks ? c + 2 : 0), ca); max_chunk(cb, c + 1);
+      }
+      if ((tid & 127) == 0) TR(n, 7);
+      {
+        const float vmax = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+        if (right) {
+          const float row_scale = g.sm_scale / ((it.first ? 1.0f : vec[row & (kRowsPer - 1)]) + kEps);
+          const float top = fmaxf(vmax * row_scale, kEps);  // lower clamp on the row maximum
+          mul = row_scale * kLog2e;
+          noff = -top * kLog2e;
+        } else {
+          noff = -vmax * kLog2e;
+        }
+      }
+      const float2 mulv = make_float2(mul, mul), noffv = make_float2(noff, noff);
+      float2 sum_a = make_float2(0.f, 0.f), sum_b = sum_a, ent_a = sum_a, ent_b = sum_a;
+      auto exp_chunk = [&](float (&x)[32], int c) {
+        logits(x, c);
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const float2 ua = fma2(make_float2(x[i], x[i + 1]), mulv, noffv);
+          const float2 ub = fma2(make_float2(x[i + 2], x[i + 3]), mulv, noffv);
+          const float2 ea = make_float2(ex2(ua.x), ex2(ua.y)), eb = make_float2(ex2(ub.x), ex2(ub.y));
+          sum_a = add2(sum_a, ea);
+          sum_b = add2(sum_b, eb);
+          ent_a = fma2(ea, ua, ent_a);
+          ent_b = fma2(eb, ub, ent_b);
+          x[i] = ea.x; x[i + 1] = ea.y; x[i + 2] = eb.x; x[i + 3] = eb.y;
+        }
+        tmem_st32(tmem_row + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&x[0]));
+      };
+#pragma unroll 1
+      for (int c = 0; c < kChunks; c += 2) {
+        tmem_wait_ld(ca); tmem_ld32_nowait(tmem_row + 32 * (c + 1), cb); exp_chunk(ca, c);
+        tmem_wait_ld(cb);
+        if (c + 2 < kChunks) tmem_ld32_nowait(tmem_row + 32 * (c + 2), ca);
+        exp_chunk(cb, c + 1);
+      }
+      const float row_sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
+      if (right) {
+        const float row_ent = (ent_a.x + ent_a.y) + (ent_b.x + ent_b.y);
+        const float denom = row_sum + kEps;
+        inv = __frcp_rn(denom);
+        // sum_i r_i ln r_i with r_i = e_i / denom and ln e_i = ln2 * u_i
+        stat = (kLn2 * row_ent - __logf(denom) * row_sum) * inv;
+      } else {
+        inv = __frcp_rn(row_sum);
+      }
+      // cl of the row for the epilogue group.  The 4-deep ring cannot be overrun: the first contraction
+      // of item n+4 needs the S buffer of item n+1, which its second contraction frees, which needs O
+      // free, i.e. the epilogue of item n past its read of this entry.
+      reinterpret_cast<float*>(base_ptr + kOffStats)[(n & 3) * 128 + row] = stat;
+      mbar_arrive(bar(kBarStat + (n & 3)));
+      if ((tid & 127) == 0) TR(n, 8);
+      const float2 invv = make_float2(inv, inv);
+      tmem_wait_st();  // the exponentials are in tensor memory
+      const bool to_smem = it.kind == kStageLeft;
+      if (to_smem && it.p_dist > 0) {
+        // P^T goes through shared memory (MN-major A operand): rounded P in tiles 9, 10 of the ring, the
+        // rounded remainder P - round(P) in tiles 11, 12.  Wait until the item that used the region last
+        // has completed its second contraction.
+        const int m = n - it.p_dist;
+        if (!mbar_wait_abortable(bar(kBarInEmpty + m % kSlots), (uint32_t)(m / kSlots) & 1u, abort_flag)) { give_up(403); break; }
+      }
+      const uint32_t sP = base + kOffPreg;
+      auto norm_chunk = [&](float (&x)[32], int c) {
+        uint32_t hi[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float2 r = mul2(make_float2(x[2 * i], x[2 * i + 1]), invv);
+          hi[i] = pack2<T>(r.x, r.y);
+          if (to_smem) {  // keep the remainder in place of the value
+            const float2 d = sub2(r, unpack2<T>(hi[i]));
+            x[2 * i] = d.x; x[2 * i + 1] = d.y;
+          }
+        }
+        if (!to_smem) {
+          // P = round(e / sum): cells 16 c .. 16 c + 15 of the row's half of the A operand (they lie over
+          // columns of S that have been read already)
+          tmem_st16(tmem_s + 32 * h0 + 16 * c, hi);
+        } else {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const int c8 = 4 * c + q4;  // 8-column group of the row's own columns
+            const uint32_t off = (uint32_t)(h0 + (c8 >> 3)) * kTileBytes + swz(row, c8 & 7);
+            st_shared_v4(sP + off, hi[4 * q4], hi[4 * q4 + 1], hi[4 * q4 + 2], hi[4 * q4 + 3]);
+            st_shared_v4(sP + 2 * kTileBytes + off, pack2<T>(x[8 * q4], x[8 * q4 + 1]), pack2<T>(x[8 * q4 + 2], x[8 * q4 + 3]),
+                         pack2<T>(x[8 * q4 + 4], x[8 * q4 + 5]), pack2<T>(x[8 * q4 + 6], x[8 * q4 + 7]));
+          }
+        }
+      };
+      tmem_ld32_nowait(tmem_row, ca);
+#pragma unroll 1
+      for (int c = 0; c < kChunks; c += 2) {
+        tmem_wait_ld(ca); tmem_ld32_nowait(tmem_row + 32 * (c + 1), cb); norm_chunk(ca, c);
+        tmem_wait_ld(cb);
+        if (c + 2 < kChunks) tmem_ld32_nowait(tmem_row + 32 * (c + 2), ca);
+        norm_chunk(cb, c + 1);
+      }
+      if (per > 1) {  // the other half of P is zero
+        if (!to_smem) {
+          uint32_t z[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) z[i] = 0u;
+          tmem_st32(tmem_s + 32 * (1 - h0), z);
+        } else {
+#pragma unroll
+          for (int c8 = 0; c8 < 8; ++c8) {
+            const uint32_t off = (uint32_t)(1 - h0) * kTileBytes + swz(row, c8);
+            st_shared_v4(sP + off, 0u, 0u, 0u, 0u);
+            st_shared_v4(sP + 2 * kTileBytes + off, 0u, 0u, 0u, 0u);
+          }
+        }
+      }
+      if (!to_smem) {
+        tmem_wait_st();
+        tc_fence_before();
+      } else {
+        fence_async_smem();
+      }
+#else
       // The row's own columns of S, read once and kept in registers.
       float s[kCols];
 #pragma unroll
@@ -573,12 +801,23 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         tmem_ld32_nowait(tmem_s + 64 * h0 + 32 * c, *reinterpret_cast<float(*)[32]>(&s[32 * c]));
 #pragma unroll
       for (int c = 0; c < kCols / 32; ++c) tmem_wait_ld(*reinterpret_cast<float(*)[32]>(&s[32 * c]));
+      if ((tid & 127) == 0) TR(n, 7);
 
       float stat = 0.f, inv;
+#ifdef MA_EXP_NOSOFTMAX
+      inv = s[0] + s[kCols - 1];
+      if (inv == 12345.678f) reinterpret_cast<float*>(base_ptr + kOffStats)[row] = inv;
+      mbar_arrive(bar(kBarStat + (n & 3)));
+      tc_fence_before();
+      mbar_arrive(bar(kBarPFull + sb));
+      continue;
+#endif
+      // Pass 1: row maximum.  Right-factor stages: of S itself (rounding is monotonic, so the maximum of
+      // the rounded logits is the rounded maximum).  Left-factor / output stages: the logits
+      // round(S) - cl[m] are formed in place first.
+      float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+      float mul, noff, row_sum;
       if (right) {
-        // x = sm_scale * round(S) / (cr + eps); the maximum of the rounded values is the rounded maximum
-        const float row_scale = g.sm_scale / ((it.first ? 1.0f : vec[row & (kRowsPer - 1)]) + kEps);
-        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
         for (int i = 0; i < kCols; i += 8) {
           m0 = max3(m0, s[i], s[i + 1]);
@@ -587,8 +826,13 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           m3 = max3(m3, s[i + 6], s[i + 7]);
         }
         const float vmax = round_through<T>(fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
-        const float top = fmaxf(vmax * row_scale, kEps);  // lower clamp on the row maximum
-        const float mul = row_scale * kLog2e, noff = -top * kLog2e;
+        if ((tid & 127) == 0) TR(n, 3);
+        // x = sm_scale * round(S) / (cr + eps), clamp on the row maximum from below
+        const float row_scale = g.sm_scale / ((it.first ? 1.0f : vec[row & (kRowsPer - 1)]) + kEps);
+        const float top = fmaxf(vmax * row_scale, kEps);
+        mul = row_scale * kLog2e;
+        noff = -top * kLog2e;
+        // Pass 2: e = 2^(mul * round(S) - off) in place, row sum, sum of e * log2(e)
         const float2 mulv = make_float2(mul, mul), noffv = make_float2(noff, noff);
         float2 sum_a = make_float2(0.f, 0.f), sum_b = sum_a, ent_a = sum_a, ent_b = sum_a;
 #pragma unroll
@@ -602,15 +846,16 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           ent_b = fma2(eb, ub, ent_b);
           s[i] = ea.x; s[i + 1] = ea.y; s[i + 2] = eb.x; s[i + 3] = eb.y;
         }
-        const float row_sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
+        row_sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
         const float row_ent = (ent_a.x + ent_a.y) + (ent_b.x + ent_b.y);
         const float denom = row_sum + kEps;
         inv = __frcp_rn(denom);
         // sum_i r_i ln r_i with r_i = e_i / denom and ln e_i = ln2 * u_i
         stat = (kLn2 * row_ent - __logf(denom) * row_sum) * inv;
+        // al = sm_scale * (P k): the scale is a power of two (D = 64), so it can ride on P exactly; the
+        // stage with V keeps P unscaled (y = P v) and scales the al half in the epilogue
+        if (it.kind == kStageRight) inv *= g.sm_scale;
       } else {
-        // w = round(S) - cl[m], softmax over m
-        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
         for (int i = 0; i < kCols; i += 8) {
           const float4 c0 = *reinterpret_cast<const float4*>(vec + i);
@@ -626,7 +871,9 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           s[i] = a.x; s[i + 1] = a.y; s[i + 2] = b.x; s[i + 3] = b.y;
           s[i + 4] = c.x; s[i + 5] = c.y; s[i + 6] = d.x; s[i + 7] = d.y;
         }
-        const float noff = -fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * kLog2e;
+        if ((tid & 127) == 0) TR(n, 3);
+        noff = -fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * kLog2e;
+        // Pass 2: e = 2^(log2e * w - off) in place, row sum
         const float2 mulv = make_float2(kLog2e, kLog2e), noffv = make_float2(noff, noff);
         float2 sum_a = make_float2(0.f, 0.f), sum_b = sum_a;
 #pragma unroll
@@ -638,7 +885,8 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           sum_b = add2(sum_b, eb);
           s[i] = ea.x; s[i + 1] = ea.y; s[i + 2] = eb.x; s[i + 3] = eb.y;
         }
-        inv = __frcp_rn((sum_a.x + sum_a.y) + (sum_b.x + sum_b.y));
+        row_sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
+        inv = __frcp_rn(row_sum);
       }
       // cl of the row for the epilogue group.  The 4-deep ring cannot be overrun: the first contraction
       // of item n+4 needs the S buffer of item n+1, which its second contraction frees, which needs O
@@ -647,8 +895,9 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       mbar_arrive(bar(kBarStat + (n & 3)));
 
       const float2 invv = make_float2(inv, inv);
+      if ((tid & 127) == 0) TR(n, 8);
       if (it.kind != kStageLeft) {
-        // P = round(e / sum) over S in tensor memory: A operand of the second contraction
+        // Pass 3: P = round(e / sum) over S in tensor memory: A operand of the second contraction
         uint32_t pk[32];
 #pragma unroll
         for (int c = 0; c < kCols / 64; ++c) {
@@ -670,8 +919,8 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         // P^T goes through shared memory (MN-major A operand): rounded P in tiles 9, 10 of the ring, the
         // rounded remainder P - round(P) in tiles 11, 12.  Wait until the item that used the region last
         // has completed its second contraction.
-        if (p_dist > 0) {
-          const int m = n - p_dist;
+        if (it.p_dist > 0) {
+          const int m = n - it.p_dist;
           if (!mbar_wait_abortable(bar(kBarInEmpty + m % kSlots), (uint32_t)(m / kSlots) & 1u, abort_flag)) { give_up(403); break; }
         }
         const uint32_t sP = base + kOffPreg;
@@ -699,7 +948,9 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         }
         fence_async_smem();
       }
+#endif
       mbar_arrive(bar(kBarPFull + sb));
+      if ((tid & 127) == 0) TR(n, 9);
     }
   }
 
@@ -707,6 +958,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
   tc_fence_before();
   __syncthreads();
   if (warp == kMma1Warp) {
+    __syncwarp();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
   }
 }
@@ -793,6 +1045,9 @@ cudaError_t launch_fused(const TcPlan* plan, const Geometry& g, int* counters, i
     const int tiles = g.N / kTile;
     int want = 1 + (7 * kTile + tiles - 1) / tiles;  // (want - 1) * tiles >= 7 * 128 items
     if (want < 8) want = 8;
+#ifdef MA_GROUP
+    want = MA_GROUP;
+#endif
     a.group = g.E * g.H < want ? g.E * g.H : want;
   }
   a.wait_deps = wait_deps;
@@ -800,6 +1055,12 @@ cudaError_t launch_fused(const TcPlan* plan, const Geometry& g, int* counters, i
   a.spin_limit = g_spin_limit_override > 0 ? g_spin_limit_override : (1 << 24);
   a.counters = counters;
   a.host_status = host_status_dev;
+#ifdef MA_TRACE
+  a.trace = nullptr;
+  if (const char* t = getenv("MA_B200_TRACE_PTR")) a.trace = reinterpret_cast<long long*>(strtoull(t, nullptr, 16));
+  if (const char* t = getenv("MA_B200_TRACE_STAGE"))
+    if (!(wait_deps == 0 && stage_begin == atoi(t))) a.trace = nullptr;
+#endif
   const int total = (stage_end - stage_begin) * (g.N / kTile) * g.E * g.H;
   const int grid = total < sms ? total : sms;
   void* params[] = {(void*)&plan->maps, (void*)&g, (void*)&a};

@@ -182,7 +182,13 @@ def test_stage_state_matches_oracle(ma, name, kernel):
     dt = case["dtype"]
     fro_lim = {"f32": 1e-4, "bf16": 1e-2, "f16": 4e-3}[dt]
     report = {}
-    for key in ("ar", "cr", "al", "cl", "y"):
+    keys = ("ar", "cr", "al", "cl", "y") if case["T"] > 1 else ("al", "cl", "y")
+    if kernel == 2:
+        # the single-launch kernel drops the lines of ar, al and y from L2 once their one reader has
+        # read them (they are never written back), so only the fp32 vectors survive the call; the same
+        # kernel launched per stage (kernel 3) keeps everything and is compared in full
+        keys = tuple(k_ for k_ in keys if k_ in ("cr", "cl"))
+    for key in keys:
         want = getattr(st_ref, key)
         want = want.reshape(-1, *want.shape[2:]).double().numpy()
         got = st[key].double().cpu().numpy()
