@@ -80,18 +80,20 @@ constexpr int kThreads = 16 * 32;
 constexpr int kRingTiles = 13;
 constexpr int kRingLeft = 9;
 constexpr int kSlots = 8;  // items in flight: depth of the per-item barrier / row-vector rings
-// Tensor memory: three S accumulators (columns 0, 128, 256); P (16-bit pairs) is written over the
-// first 64 columns of its S.  One O accumulator (column 384): the epilogue empties it much faster
-// than items arrive.
+// Tensor memory: three 128-column accumulator buffers (columns 0, 128, 256): item n's S = A B^T goes to
+// buffer n % 3, the softmax reads it, and the second contraction writes the item's O over it, so that S
+// and O of an item share a buffer and three items can be between the first contraction and the
+// epilogue.  P (16-bit pairs, 64 columns) has two buffers of its own (columns 384, 448), one per softmax
+// group.
 constexpr int kSBuffers = 3;
-constexpr uint32_t kTmemO = 384;
+constexpr uint32_t kTmemP = 384;
 constexpr uint32_t kOffSlots = 0;
 constexpr uint32_t kOffPreg = kRingLeft * kTileBytes;             // P region = ring tiles 9..12
 constexpr uint32_t kOffOnes = kRingTiles * kTileBytes;            // 16 x 128 K-major operand of ones (4 KB)
 constexpr uint32_t kOffVec = kOffOnes + 4096;                     // kSlots x 512 B (cr or cl of the item)
 constexpr uint32_t kOffStats = kOffVec + kSlots * 512;            // 4 x 128 floats (cl of the item's rows)
 constexpr uint32_t kOffBar = kOffStats + 4 * 128 * 4;
-constexpr int kNumBarsConst = 48;
+constexpr int kNumBarsConst = 56;
 constexpr int kDescRing = 16;  // item descriptors; deeper than the planner can run ahead (kSlots)
 constexpr uint32_t kOffDesc = kOffBar + 8 * kNumBarsConst + 16;
 constexpr uint32_t kSmemUsed = kOffDesc + 16 * kDescRing;
@@ -105,14 +107,14 @@ enum {
   kBarInEmpty = 8,    // [8] operand tiles of an item released by the second contraction
   kBarPlan = 16,      // [8] descriptor of an item written by the planner
   kBarSFull = 24,     // [3] S accumulator ready
-  kBarSEmpty = 27,    // [3] S / P released by the second contraction
-  kBarPFull = 30,     // [3] P written (tensor memory, or shared memory in the left-factor stage)
-  kBarOFull = 33,     // [1] O accumulator ready
-  kBarOEmpty = 34,    // [1] O accumulator read by the epilogue group
-  kBarStat = 36,      // [4] row statistics of the item written by its softmax group
-  kBarDone = 40,      // [4] item stored to global memory by all 128 epilogue threads
-  kBarPubFree = 44,   // [4] completion of that item published
-  kNumBars = 48
+  kBarSEmpty = 27,    // [3] accumulator buffer (S, then O) read by the epilogue group
+  kBarOFull = 30,     // [3] O accumulator ready
+  kBarPFull = 33,     // [2] P written (tensor memory, or shared memory in the left-factor stage)
+  kBarPEmpty = 35,    // [2] P consumed by the second contraction
+  kBarStat = 37,      // [4] row statistics of the item written by its softmax group      // [4] row statistics of the item written by its softmax group
+  kBarDone = 41,      // [4] item stored to global memory by all 128 epilogue threads
+  kBarPubFree = 45,   // [4] completion of that item published
+  kNumBars = 49
 };
 static_assert(kNumBars <= kNumBarsConst, "barrier count");
 constexpr int kEpilogueBarrier = 1;  // named barriers of the 128 epilogue threads: this one and the next
@@ -138,12 +140,27 @@ struct Item {
 // the storage type before the fp32 softmax arithmetic, ma/ma_torch.py:11, :27, :56).
 // Done on the FMA pipe (Veltkamp split with the constant 2^(24-p) + 1 for a p-bit significand: the high
 // part is x rounded to nearest at p bits), because the conversion instructions share a pipe with the
-// exponentials, which is the busiest one of this kernel.
+// exponentials, which is the busiest one of this kernel.  The product is formed with scalar mul.rn: the
+// packed form was contracted with the subtraction into one fused multiply-add, which undoes the rounding.
+__device__ __forceinline__ float mul_rn(float a, float b) {
+  float d;
+  asm("mul.rn.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+  return d;
+}
 template <typename T>
 __device__ __forceinline__ float2 round2(float2 x) {
   constexpr float c = std::is_same<T, __nv_bfloat16>::value ? 65537.0f : 8193.0f;
-  const float2 big = mul2(x, make_float2(c, c));
+  const float2 big = make_float2(mul_rn(x.x, c), mul_rn(x.y, c));
   return add2(big, sub2(x, big));
+}
+// 16-bit pair -> fp32 pair without a conversion instruction where the format allows it
+template <typename T>
+__device__ __forceinline__ float2 widen2(uint32_t u) {
+  return unpack2<T>(u);
+}
+template <>
+__device__ __forceinline__ float2 widen2<__nv_bfloat16>(uint32_t u) {
+  return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
 }
 
 __device__ __forceinline__ void red_release_add(int* p, int v) {
@@ -184,11 +201,13 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
     }
     for (int i = 0; i < kSBuffers; ++i) {
       mbar_init(bar(kBarSFull + i), 1);
-      mbar_init(bar(kBarSEmpty + i), 1);
-      mbar_init(bar(kBarPFull + i), 128);
+      mbar_init(bar(kBarSEmpty + i), 128);
+      mbar_init(bar(kBarOFull + i), 1);
     }
-    mbar_init(bar(kBarOFull), 1);
-    mbar_init(bar(kBarOEmpty), 128);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(kBarPFull + i), 128);
+      mbar_init(bar(kBarPEmpty + i), 1);
+    }
     for (int i = 0; i < 4; ++i) {
       mbar_init(bar(kBarStat + i), 128);
       mbar_init(bar(kBarDone + i), 128);
@@ -248,6 +267,11 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
   // 256 x 192 + 128 x 80 + 128 x 48 = 65536 = 512 x 128, so the increase can always be granted.
   // (What setmaxnreg redistributes is the allocation the CTA was launched with - threads x registers
   // per thread - not the whole register file: a request beyond that pool blocks for ever.)
+#ifdef MA_EXP_POLITE
+#define ROLE_WAIT(b_, p_) mbar_wait_polite(b_, p_, abort_flag, MA_EXP_POLITE)
+#else
+#define ROLE_WAIT(b_, p_) mbar_wait_abortable(b_, p_, abort_flag)
+#endif
   if (warp >= kPlannerWarp) {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
   if (warp == kPlannerWarp) {
@@ -337,7 +361,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
             if (pos + ntiles > limit) { sk = kRingTiles - pos; pos = 0; }
             if (free_tiles >= ntiles + sk && n - oldest < kSlots) { t0 = pos; charged = ntiles + sk; break; }
             // items whose second contraction has completed give their tiles back (in order)
-            if (!mbar_wait_abortable(bar(kBarInEmpty + oldest % kSlots), (uint32_t)(oldest / kSlots) & 1u, abort_flag)) {
+            if (!ROLE_WAIT(bar(kBarInEmpty + oldest % kSlots), (uint32_t)(oldest / kSlots) & 1u)) {
               give_up(202);
               ok = false;
               break;
@@ -373,7 +397,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       int issued = 0;
       for (int n = 0; n < n_items; ++n) {
         const int slot = n % kSlots;
-        if (!mbar_wait_abortable(bar(kBarPlan + slot), (uint32_t)(n / kSlots) & 1u, abort_flag)) break;  // the planner gave up
+        if (!ROLE_WAIT(bar(kBarPlan + slot), (uint32_t)(n / kSlots) & 1u)) break;  // the planner gave up
         const Item it = read_item(n);
         const bool right = it.kind == kStageRight || it.kind == kStageRightWithV;
         const bool three = it.kind == kStageRightWithV || it.kind == kStageOutput;
@@ -427,9 +451,9 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       constexpr uint32_t idesc1 = instr_desc(kFmt, 0, 0, kTile, kTile);
       for (int n = 0; n < n_items; ++n) {
         const int slot = n % kSlots, sb = n % kSBuffers;
-        if (!mbar_wait_abortable(bar(kBarInFull + slot), (uint32_t)(n / kSlots) & 1u, abort_flag)) { give_up(301); break; }
+        if (!ROLE_WAIT(bar(kBarInFull + slot), (uint32_t)(n / kSlots) & 1u)) { give_up(301); break; }
         const int t0 = read_item(n).t0;
-        if (!mbar_wait_abortable(bar(kBarSEmpty + sb), ((uint32_t)(n / kSBuffers) & 1u) ^ 1u, abort_flag)) { give_up(302); break; }
+        if (!ROLE_WAIT(bar(kBarSEmpty + sb), ((uint32_t)(n / kSBuffers) & 1u) ^ 1u)) { give_up(302); break; }
         tc_fence_after();
         const uint32_t dA = dA0 + t0 * kTileStep, dB = dA + kTileStep;
 #pragma unroll
@@ -443,7 +467,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       // takes about a microsecond: a thread of its own keeps that off the epilogue group's path.  (The
       // output stage is consumed only when state slots are reused, by the next head in the slot.)
       for (int n = 0; n < n_items; ++n) {
-        if (!mbar_wait_abortable(bar(kBarDone + (n & 3)), (uint32_t)(n >> 2) & 1u, abort_flag)) { give_up(601); break; }
+        if (!ROLE_WAIT(bar(kBarDone + (n & 3)), (uint32_t)(n >> 2) & 1u)) { give_up(601); break; }
         const Item it = read_item(n);
         if (it.stage != nst_all - 1 || args.reuse_slots) {
           __threadfence();
@@ -460,16 +484,15 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       const uint32_t dTmn0 = smem_desc_lo(base + kOffSlots, kTileBytes);   // ring tile 0 as an MN-major operand
       constexpr uint32_t kTileStep = kTileBytes >> 4;
       for (int n = 0; n < n_items; ++n) {
-        const int sb = n % kSBuffers, slot = n % kSlots;
-        if (!mbar_wait_abortable(bar(kBarPFull + sb), (uint32_t)(n / kSBuffers) & 1u, abort_flag)) { give_up(303); break; }
+        const int sb = n % kSBuffers, slot = n % kSlots, pb = n & 1;
+        if (!ROLE_WAIT(bar(kBarPFull + pb), (uint32_t)(n >> 1) & 1u)) { give_up(303); break; }
         TR(n, 10);
         const Item it = read_item(n);
         const int kind = it.kind;
-        if (!mbar_wait_abortable(bar(kBarOEmpty), ((uint32_t)n & 1u) ^ 1u, abort_flag)) { give_up(304); break; }
         tc_fence_after();
         // tiles of the item: A, B, V
         const uint32_t dA = dTmn0 + it.t0 * kTileStep, dB = dA + kTileStep, dV = dB + kTileStep;
-        const uint32_t tmem_o = tmem + kTmemO, tmem_p = tmem + sb * 128;
+        const uint32_t tmem_o = tmem + sb * 128, tmem_p = tmem + kTmemP + pb * 64;  // O goes over the item's S
         if (kind == kStageRight) {
           constexpr uint32_t idesc = instr_desc(kFmt, 0, 1, kHead, kTile);
 #pragma unroll
@@ -496,8 +519,8 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
 #pragma unroll
           for (int kk = 0; kk < kTile / 16; ++kk) mma_f16_ts(tmem_o, tmem_p + kk * 8, dV + kk * 128, idesc, kk > 0);
         }
-        mma_commit(bar(kBarOFull));
-        mma_commit(bar(kBarSEmpty + sb));
+        mma_commit(bar(kBarOFull + sb));
+        mma_commit(bar(kBarPEmpty + pb));
         mma_commit(bar(kBarInEmpty + slot));
         TR(n, 12);
       }
@@ -510,8 +533,9 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const unsigned long long pol_first = l2_policy_evict_first();
     for (int n = 0; n < n_items; ++n) {
-      const bool got = mbar_wait_abortable(bar(kBarStat + (n & 3)), (uint32_t)(n >> 2) & 1u, abort_flag) &&
-                       mbar_wait_abortable(bar(kBarOFull), (uint32_t)n & 1u, abort_flag);
+      const int sb = n % kSBuffers;
+      const bool got = ROLE_WAIT(bar(kBarStat + (n & 3)), (uint32_t)(n >> 2) & 1u) &&
+                       ROLE_WAIT(bar(kBarOFull + sb), (uint32_t)(n / kSBuffers) & 1u);
       // all 128 threads leave together or not at all (a thread that went on alone would strand the
       // others at the group barrier below)
       if (named_barrier_or(kEpilogueBarrier, 128, !got)) {
@@ -522,7 +546,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       if (tid == 256) TR(n, 13);
       const Item it = read_item(n);
       const float stat = reinterpret_cast<const float*>(base_ptr + kOffStats)[(n & 3) * 128 + row];
-      const uint32_t tmem_o = tmem + lane_base + kTmemO;
+      const uint32_t tmem_o = tmem + lane_base + sb * 128;
       T* dst0;
       // Row of the tile -> (row within its block or column, which of the tile's `per` blocks / columns).
       // Right-factor tiles hold blocks one after the other (row = blk*B + j); the accumulator of the
@@ -583,7 +607,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       }
 #endif
       tc_fence_before();
-      mbar_arrive(bar(kBarOEmpty));
+      mbar_arrive(bar(kBarSEmpty + sb));  // the accumulator buffer may take the S of item n + 3
       if (tid == 256) TR(n, 5);
       if (args.wait_deps) {
         // The state tiles this item read (each is written once and read once) are dead: drop their lines
@@ -602,7 +626,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         asm volatile("fence.proxy.async.global;" ::: "memory");
         if (tid == 256) TR(n, 4);
         // hand the item to the publisher (4-deep ring)
-        if (!mbar_wait_abortable(bar(kBarPubFree + (n & 3)), ((uint32_t)(n >> 2) & 1u) ^ 1u, abort_flag)) give_up(502);
+        if (!ROLE_WAIT(bar(kBarPubFree + (n & 3)), ((uint32_t)(n >> 2) & 1u) ^ 1u)) give_up(502);
         mbar_arrive(bar(kBarDone + (n & 3)));
       }
       if (tid == 256) TR(n, 14);
@@ -619,7 +643,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
     // P is zero.
     const int h0 = per > 1 ? (row >> 6) : 0;  // uniform within a warp
     for (int n = grp; n < n_items; n += 2) {
-      const int slot = n % kSlots, sb = n % kSBuffers;
+      const int slot = n % kSlots, sb = n % kSBuffers, pb = n & 1;  // pb = this group's P buffer
       const float* vec = reinterpret_cast<const float*>(base_ptr + kOffVec + slot * 512) + (per > 1 ? 64 * h0 : 0);
       if (!mbar_wait_abortable(bar(kBarInFull + slot), (uint32_t)(n / kSlots) & 1u, abort_flag)) { give_up(401); break; }
       const Item it = read_item(n);
@@ -629,171 +653,6 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       if ((tid & 127) == 0) TR(n, 6);
       const uint32_t tmem_s = tmem + lane_base + sb * 128;
 
-#ifdef MA_ROLLED
-      // Three passes over the row's own columns of S, each a short loop over 32-column chunks read from
-      // tensor memory one chunk ahead of the arithmetic (two register buffers): maximum; exponentials,
-      // row sum and entropy, the exponentials written back over S as fp32; normalised factor, rounded,
-      // over the first half of S as the A operand of the second contraction.  The loops are kept rolled
-      // so that the code of all roles of the CTA stays resident in the instruction caches.
-      constexpr int kChunks = kCols / 32;
-      const uint32_t tmem_row = tmem_s + 64 * h0;
-      float ca[32], cb[32];
-      float stat = 0.f, inv;
-      float mul = kLog2e, noff;
-      // logits of a chunk up to a positive row factor:  right-factor stages round(S), others round(S) - cl[m]
-      auto logits = [&](float (&x)[32], int c) {
-        if (right) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float2 a = round2<T>(make_float2(x[i], x[i + 1]));
-            x[i] = a.x; x[i + 1] = a.y;
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float4 c4 = *reinterpret_cast<const float4*>(vec + 32 * c + i);
-            const float2 a = sub2(round2<T>(make_float2(x[i], x[i + 1])), make_float2(c4.x, c4.y));
-            const float2 b2 = sub2(round2<T>(make_float2(x[i + 2], x[i + 3])), make_float2(c4.z, c4.w));
-            x[i] = a.x; x[i + 1] = a.y; x[i + 2] = b2.x; x[i + 3] = b2.y;
-          }
-        }
-      };
-      float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
-      auto max_chunk = [&](float (&x)[32], int c) {
-        logits(x, c);
-#pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          m0 = max3(m0, x[i], x[i + 1]);
-          m1 = max3(m1, x[i + 2], x[i + 3]);
-          m2 = max3(m2, x[i + 4], x[i + 5]);
-          m3 = max3(m3, x[i + 6], x[i + 7]);
-        }
-      };
-      tmem_ld32_nowait(tmem_row, ca);
-#pragma unroll 1
-      for (int c = 0; c < kChunks; c += 2) {
-        tmem_wait_ld(ca); tmem_ld32_nowait(tmem_row + 32 * (c + 1), cb); max_chunk(ca, c);
-        tmem_wait_ld(cb); tmem_ld32_nowait(tmem_row + 32 * (c + 2 < kChunks ? c + 2 : 0), ca); max_chunk(cb, c + 1);
-      }
-      if ((tid & 127) == 0) TR(n, 7);
-      {
-        const float vmax = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-        if (right) {
-          const float row_scale = g.sm_scale / ((it.first ? 1.0f : vec[row & (kRowsPer - 1)]) + kEps);
-          const float top = fmaxf(vmax * row_scale, kEps);  // lower clamp on the row maximum
-          mul = row_scale * kLog2e;
-          noff = -top * kLog2e;
-        } else {
-          noff = -vmax * kLog2e;
-        }
-      }
-      const float2 mulv = make_float2(mul, mul), noffv = make_float2(noff, noff);
-      float2 sum_a = make_float2(0.f, 0.f), sum_b = sum_a, ent_a = sum_a, ent_b = sum_a;
-      auto exp_chunk = [&](float (&x)[32], int c) {
-        logits(x, c);
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          const float2 ua = fma2(make_float2(x[i], x[i + 1]), mulv, noffv);
-          const float2 ub = fma2(make_float2(x[i + 2], x[i + 3]), mulv, noffv);
-          const float2 ea = make_float2(ex2(ua.x), ex2(ua.y)), eb = make_float2(ex2(ub.x), ex2(ub.y));
-          sum_a = add2(sum_a, ea);
-          sum_b = add2(sum_b, eb);
-          ent_a = fma2(ea, ua, ent_a);
-          ent_b = fma2(eb, ub, ent_b);
-          x[i] = ea.x; x[i + 1] = ea.y; x[i + 2] = eb.x; x[i + 3] = eb.y;
-        }
-        tmem_st32(tmem_row + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&x[0]));
-      };
-#pragma unroll 1
-      for (int c = 0; c < kChunks; c += 2) {
-        tmem_wait_ld(ca); tmem_ld32_nowait(tmem_row + 32 * (c + 1), cb); exp_chunk(ca, c);
-        tmem_wait_ld(cb);
-        if (c + 2 < kChunks) tmem_ld32_nowait(tmem_row + 32 * (c + 2), ca);
-        exp_chunk(cb, c + 1);
-      }
-      const float row_sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
-      if (right) {
-        const float row_ent = (ent_a.x + ent_a.y) + (ent_b.x + ent_b.y);
-        const float denom = row_sum + kEps;
-        inv = __frcp_rn(denom);
-        // sum_i r_i ln r_i with r_i = e_i / denom and ln e_i = ln2 * u_i
-        stat = (kLn2 * row_ent - __logf(denom) * row_sum) * inv;
-      } else {
-        inv = __frcp_rn(row_sum);
-      }
-      // cl of the row for the epilogue group.  The 4-deep ring cannot be overrun: the first contraction
-      // of item n+4 needs the S buffer of item n+1, which its second contraction frees, which needs O
-      // free, i.e. the epilogue of item n past its read of this entry.
-      reinterpret_cast<float*>(base_ptr + kOffStats)[(n & 3) * 128 + row] = stat;
-      mbar_arrive(bar(kBarStat + (n & 3)));
-      if ((tid & 127) == 0) TR(n, 8);
-      const float2 invv = make_float2(inv, inv);
-      tmem_wait_st();  // the exponentials are in tensor memory
-      const bool to_smem = it.kind == kStageLeft;
-      if (to_smem && it.p_dist > 0) {
-        // P^T goes through shared memory (MN-major A operand): rounded P in tiles 9, 10 of the ring, the
-        // rounded remainder P - round(P) in tiles 11, 12.  Wait until the item that used the region last
-        // has completed its second contraction.
-        const int m = n - it.p_dist;
-        if (!mbar_wait_abortable(bar(kBarInEmpty + m % kSlots), (uint32_t)(m / kSlots) & 1u, abort_flag)) { give_up(403); break; }
-      }
-      const uint32_t sP = base + kOffPreg;
-      auto norm_chunk = [&](float (&x)[32], int c) {
-        uint32_t hi[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float2 r = mul2(make_float2(x[2 * i], x[2 * i + 1]), invv);
-          hi[i] = pack2<T>(r.x, r.y);
-          if (to_smem) {  // keep the remainder in place of the value
-            const float2 d = sub2(r, unpack2<T>(hi[i]));
-            x[2 * i] = d.x; x[2 * i + 1] = d.y;
-          }
-        }
-        if (!to_smem) {
-          // P = round(e / sum): cells 16 c .. 16 c + 15 of the row's half of the A operand (they lie over
-          // columns of S that have been read already)
-          tmem_st16(tmem_s + 32 * h0 + 16 * c, hi);
-        } else {
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            const int c8 = 4 * c + q4;  // 8-column group of the row's own columns
-            const uint32_t off = (uint32_t)(h0 + (c8 >> 3)) * kTileBytes + swz(row, c8 & 7);
-            st_shared_v4(sP + off, hi[4 * q4], hi[4 * q4 + 1], hi[4 * q4 + 2], hi[4 * q4 + 3]);
-            st_shared_v4(sP + 2 * kTileBytes + off, pack2<T>(x[8 * q4], x[8 * q4 + 1]), pack2<T>(x[8 * q4 + 2], x[8 * q4 + 3]),
-                         pack2<T>(x[8 * q4 + 4], x[8 * q4 + 5]), pack2<T>(x[8 * q4 + 6], x[8 * q4 + 7]));
-          }
-        }
-      };
-      tmem_ld32_nowait(tmem_row, ca);
-#pragma unroll 1
-      for (int c = 0; c < kChunks; c += 2) {
-        tmem_wait_ld(ca); tmem_ld32_nowait(tmem_row + 32 * (c + 1), cb); norm_chunk(ca, c);
-        tmem_wait_ld(cb);
-        if (c + 2 < kChunks) tmem_ld32_nowait(tmem_row + 32 * (c + 2), ca);
-        norm_chunk(cb, c + 1);
-      }
-      if (per > 1) {  // the other half of P is zero
-        if (!to_smem) {
-          uint32_t z[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) z[i] = 0u;
-          tmem_st32(tmem_s + 32 * (1 - h0), z);
-        } else {
-#pragma unroll
-          for (int c8 = 0; c8 < 8; ++c8) {
-            const uint32_t off = (uint32_t)(1 - h0) * kTileBytes + swz(row, c8);
-            st_shared_v4(sP + off, 0u, 0u, 0u, 0u);
-            st_shared_v4(sP + 2 * kTileBytes + off, 0u, 0u, 0u, 0u);
-          }
-        }
-      }
-      if (!to_smem) {
-        tmem_wait_st();
-        tc_fence_before();
-      } else {
-        fence_async_smem();
-      }
-#else
       // The row's own columns of S, read once and kept in registers.
       float s[kCols];
 #pragma unroll
@@ -809,7 +668,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       if (inv == 12345.678f) reinterpret_cast<float*>(base_ptr + kOffStats)[row] = inv;
       mbar_arrive(bar(kBarStat + (n & 3)));
       tc_fence_before();
-      mbar_arrive(bar(kBarPFull + sb));
+      mbar_arrive(bar(kBarPFull + pb));
       continue;
 #endif
       // Pass 1: row maximum.  Right-factor stages: of S itself (rounding is monotonic, so the maximum of
@@ -897,7 +756,12 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       const float2 invv = make_float2(inv, inv);
       if ((tid & 127) == 0) TR(n, 8);
       if (it.kind != kStageLeft) {
-        // Pass 3: P = round(e / sum) over S in tensor memory: A operand of the second contraction
+        // Pass 3: P = round(e / sum) into the group's P buffer in tensor memory: A operand of the second
+        // contraction.  (The buffer is free once the second contraction of the group's previous item has
+        // completed - long ago, as a rule.)
+        if (!mbar_wait_abortable(bar(kBarPEmpty + pb), ((uint32_t)(n >> 1) & 1u) ^ 1u, abort_flag)) { give_up(404); break; }
+        tc_fence_after();
+        const uint32_t tmem_p = tmem + lane_base + kTmemP + pb * 64;
         uint32_t pk[32];
 #pragma unroll
         for (int c = 0; c < kCols / 64; ++c) {
@@ -906,12 +770,12 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
             const float2 r = mul2(make_float2(s[64 * c + 2 * i], s[64 * c + 2 * i + 1]), invv);
             pk[i] = pack2<T>(r.x, r.y);
           }
-          tmem_st32(tmem_s + 32 * (h0 + c), pk);
+          tmem_st32(tmem_p + 32 * (h0 + c), pk);
         }
         if (per > 1) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) pk[i] = 0u;
-          tmem_st32(tmem_s + 32 * (1 - h0), pk);
+          tmem_st32(tmem_p + 32 * (1 - h0), pk);
         }
         tmem_wait_st();
         tc_fence_before();
@@ -931,7 +795,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           for (int i = 0; i < 4; ++i) {
             const float2 r = mul2(make_float2(s[8 * c8 + 2 * i], s[8 * c8 + 2 * i + 1]), invv);
             hi[i] = pack2<T>(r.x, r.y);
-            const float2 d = sub2(r, unpack2<T>(hi[i]));
+            const float2 d = sub2(r, widen2<T>(hi[i]));
             lo[i] = pack2<T>(d.x, d.y);
           }
           const uint32_t off = (uint32_t)(h0 + (c8 >> 3)) * kTileBytes + swz(row, c8 & 7);
@@ -948,8 +812,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         }
         fence_async_smem();
       }
-#endif
-      mbar_arrive(bar(kBarPFull + sb));
+      mbar_arrive(bar(kBarPFull + pb));
       if ((tid & 127) == 0) TR(n, 9);
     }
   }
