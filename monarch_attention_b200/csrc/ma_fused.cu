@@ -92,7 +92,8 @@ constexpr uint32_t kOffPreg = kRingLeft * kTileBytes;             // P region = 
 constexpr uint32_t kOffOnes = kRingTiles * kTileBytes;            // 16 x 128 K-major operand of ones (4 KB)
 constexpr uint32_t kOffVec = kOffOnes + 4096;                     // kSlots x 512 B (cr or cl of the item)
 constexpr uint32_t kOffStats = kOffVec + kSlots * 512;            // 4 x 128 floats (cl of the item's rows)
-constexpr uint32_t kOffBar = kOffStats + 4 * 128 * 4;
+constexpr uint32_t kOffXch = kOffStats + 4 * 128 * 4;              // 2 x 3 x 2 x 128 floats exchanged between the halves of a row
+constexpr uint32_t kOffBar = kOffXch + 2 * 3 * 2 * 128 * 4;
 constexpr int kNumBarsConst = 56;
 constexpr int kDescRing = 16;  // item descriptors; deeper than the planner can run ahead (kSlots)
 constexpr uint32_t kOffDesc = kOffBar + 8 * kNumBarsConst + 16;
@@ -117,7 +118,8 @@ enum {
   kNumBars = 49
 };
 static_assert(kNumBars <= kNumBarsConst, "barrier count");
-constexpr int kEpilogueBarrier = 1;  // named barriers of the 128 epilogue threads: this one and the next
+constexpr int kEpilogueBarrier = 1;  // named barrier of the 128 epilogue threads
+constexpr int kSoftmaxBarrier = 3;   // named barriers of the 256 softmax threads: this one and the next
 
 struct FusedArgs {
   int stage_begin, stage_end;  // stages [begin, end) of the 2T stages run in this launch
@@ -205,7 +207,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       mbar_init(bar(kBarOFull + i), 1);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(bar(kBarPFull + i), 128);
+      mbar_init(bar(kBarPFull + i), 256);
       mbar_init(bar(kBarPEmpty + i), 1);
     }
     for (int i = 0; i < 4; ++i) {
@@ -633,92 +635,77 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
     }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 192;");
-    // =========================== softmax groups ==========================================
-    const int grp = warp >> 2;                      // items with local index n = grp (mod 2)
+    // =========================== softmax warps ===========================================
+    // Both groups of four warps work on the SAME item: a row's columns are split between thread `row` of
+    // group 0 and thread `row` of group 1 (warps w and w + 4 reach the same tensor-memory lanes).  All
+    // eight warps then run the same short instruction sequence at the same time - with the groups on
+    // alternating items, every scheduler had two copies of a much longer sequence in flight at different
+    // places and the warps spent more time waiting for instructions than issuing them.  The halves of a
+    // row exchange their maximum and their sums through shared memory (two 256-thread barriers per item).
+    const int grp = warp >> 2;
     const int row = (warp & 3) * 32 + lane;         // tensor-memory lane = tile row
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    // 64-column halves of the row this thread works on: both, or - with two blocks per tile - only the
-    // half that belongs to the row's own block or column (rows are blk*64 + j in the right-factor
-    // tiles and jj*64 + l in the column tiles; columns are blk*64 + i, or jj*64 + m); the other half of
-    // P is zero.
+    // With two blocks per tile only the 64-column half that belongs to the row's own block or column
+    // means anything (rows are blk*64 + j in the right-factor tiles and jj*64 + l in the column tiles;
+    // columns are blk*64 + i, or jj*64 + m); the other half of P is zero.
     const int h0 = per > 1 ? (row >> 6) : 0;  // uniform within a warp
-    for (int n = grp; n < n_items; n += 2) {
-      const int slot = n % kSlots, sb = n % kSBuffers, pb = n & 1;  // pb = this group's P buffer
-      const float* vec = reinterpret_cast<const float*>(base_ptr + kOffVec + slot * 512) + (per > 1 ? 64 * h0 : 0);
-      if (!mbar_wait_abortable(bar(kBarInFull + slot), (uint32_t)(n / kSlots) & 1u, abort_flag)) { give_up(401); break; }
-      const Item it = read_item(n);
+    constexpr int kMine = 64 / PER;           // columns of the row this thread works on
+    const int col0 = per > 1 ? 64 * h0 + 32 * grp : 64 * grp;  // first of them
+    float* xch_base = reinterpret_cast<float*>(base_ptr + kOffXch);  // [2][3][2][128]: shift, sum, entropy sum per half row
+    for (int n = 0; n < n_items; ++n) {
+      float* xch = xch_base + (n & 1) * 768;  // by item parity: a fast thread's next item must not overwrite what a slow one still reads
+      const int slot = n % kSlots, sb = n % kSBuffers, pb = n & 1;
+      const float* vec = reinterpret_cast<const float*>(base_ptr + kOffVec + slot * 512);
+      bool ok = mbar_wait_abortable(bar(kBarInFull + slot), (uint32_t)(n / kSlots) & 1u, abort_flag);
+      ok = ok && mbar_wait_abortable(bar(kBarSFull + sb), (uint32_t)(n / kSBuffers) & 1u, abort_flag);
+      Item it;
+      it.kind = kStageRight; it.first = 1; it.p_dist = 0;
+      if (ok) it = read_item(n);
       const bool right = it.kind == kStageRight || it.kind == kStageRightWithV;
-      if (!mbar_wait_abortable(bar(kBarSFull + sb), (uint32_t)(n / kSBuffers) & 1u, abort_flag)) { give_up(402); break; }
       tc_fence_after();
-      if ((tid & 127) == 0) TR(n, 6);
+      if ((tid & 255) == 0) TR(n, 6);
       const uint32_t tmem_s = tmem + lane_base + sb * 128;
 
-      // The row's own columns of S, read once and kept in registers.
-      float s[kCols];
+      // This thread's columns of S, read once and kept in registers.
+      float s[kMine];
+      if (ok) {
 #pragma unroll
-      for (int c = 0; c < kCols / 32; ++c)
-        tmem_ld32_nowait(tmem_s + 64 * h0 + 32 * c, *reinterpret_cast<float(*)[32]>(&s[32 * c]));
+        for (int c = 0; c < kMine / 32; ++c)
+          tmem_ld32_nowait(tmem_s + col0 + 32 * c, *reinterpret_cast<float(*)[32]>(&s[32 * c]));
 #pragma unroll
-      for (int c = 0; c < kCols / 32; ++c) tmem_wait_ld(*reinterpret_cast<float(*)[32]>(&s[32 * c]));
-      if ((tid & 127) == 0) TR(n, 7);
+        for (int c = 0; c < kMine / 32; ++c) tmem_wait_ld(*reinterpret_cast<float(*)[32]>(&s[32 * c]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < kMine; ++i) s[i] = 0.f;
+      }
+      if ((tid & 255) == 0) TR(n, 7);
 
-      float stat = 0.f, inv;
 #ifdef MA_EXP_NOSOFTMAX
-      inv = s[0] + s[kCols - 1];
-      if (inv == 12345.678f) reinterpret_cast<float*>(base_ptr + kOffStats)[row] = inv;
-      mbar_arrive(bar(kBarStat + (n & 3)));
+      if (s[0] + s[kMine - 1] == 12345.678f) xch_base[row] = s[0];
+      if (grp == 0) mbar_arrive(bar(kBarStat + (n & 3)));
       tc_fence_before();
       mbar_arrive(bar(kBarPFull + pb));
+      if (named_barrier_or(kSoftmaxBarrier, 256, !ok)) break;
       continue;
 #endif
-      // Pass 1: row maximum.  Right-factor stages: of S itself (rounding is monotonic, so the maximum of
-      // the rounded logits is the rounded maximum).  Left-factor / output stages: the logits
+      // Pass 1: maximum of this half row.  Right-factor stages: of S itself (rounding is monotonic, so the
+      // maximum of the rounded logits is the rounded maximum).  Left-factor / output stages: the logits
       // round(S) - cl[m] are formed in place first.
       float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
-      float mul, noff, row_sum;
       if (right) {
 #pragma unroll
-        for (int i = 0; i < kCols; i += 8) {
+        for (int i = 0; i < kMine; i += 8) {
           m0 = max3(m0, s[i], s[i + 1]);
           m1 = max3(m1, s[i + 2], s[i + 3]);
           m2 = max3(m2, s[i + 4], s[i + 5]);
           m3 = max3(m3, s[i + 6], s[i + 7]);
         }
-        const float vmax = round_through<T>(fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
-        if ((tid & 127) == 0) TR(n, 3);
-        // x = sm_scale * round(S) / (cr + eps), clamp on the row maximum from below
-        const float row_scale = g.sm_scale / ((it.first ? 1.0f : vec[row & (kRowsPer - 1)]) + kEps);
-        const float top = fmaxf(vmax * row_scale, kEps);
-        mul = row_scale * kLog2e;
-        noff = -top * kLog2e;
-        // Pass 2: e = 2^(mul * round(S) - off) in place, row sum, sum of e * log2(e)
-        const float2 mulv = make_float2(mul, mul), noffv = make_float2(noff, noff);
-        float2 sum_a = make_float2(0.f, 0.f), sum_b = sum_a, ent_a = sum_a, ent_b = sum_a;
-#pragma unroll
-        for (int i = 0; i < kCols; i += 4) {
-          const float2 ua = fma2(round2<T>(make_float2(s[i], s[i + 1])), mulv, noffv);
-          const float2 ub = fma2(round2<T>(make_float2(s[i + 2], s[i + 3])), mulv, noffv);
-          const float2 ea = make_float2(ex2(ua.x), ex2(ua.y)), eb = make_float2(ex2(ub.x), ex2(ub.y));
-          sum_a = add2(sum_a, ea);
-          sum_b = add2(sum_b, eb);
-          ent_a = fma2(ea, ua, ent_a);
-          ent_b = fma2(eb, ub, ent_b);
-          s[i] = ea.x; s[i + 1] = ea.y; s[i + 2] = eb.x; s[i + 3] = eb.y;
-        }
-        row_sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
-        const float row_ent = (ent_a.x + ent_a.y) + (ent_b.x + ent_b.y);
-        const float denom = row_sum + kEps;
-        inv = __frcp_rn(denom);
-        // sum_i r_i ln r_i with r_i = e_i / denom and ln e_i = ln2 * u_i
-        stat = (kLn2 * row_ent - __logf(denom) * row_sum) * inv;
-        // al = sm_scale * (P k): the scale is a power of two (D = 64), so it can ride on P exactly; the
-        // stage with V keeps P unscaled (y = P v) and scales the al half in the epilogue
-        if (it.kind == kStageRight) inv *= g.sm_scale;
       } else {
+        const float* cl = vec + col0;
 #pragma unroll
-        for (int i = 0; i < kCols; i += 8) {
-          const float4 c0 = *reinterpret_cast<const float4*>(vec + i);
-          const float4 c1 = *reinterpret_cast<const float4*>(vec + i + 4);
+        for (int i = 0; i < kMine; i += 8) {
+          const float4 c0 = *reinterpret_cast<const float4*>(cl + i);
+          const float4 c1 = *reinterpret_cast<const float4*>(cl + i + 4);
           const float2 a = sub2(round2<T>(make_float2(s[i], s[i + 1])), make_float2(c0.x, c0.y));
           const float2 b = sub2(round2<T>(make_float2(s[i + 2], s[i + 3])), make_float2(c0.z, c0.w));
           const float2 c = sub2(round2<T>(make_float2(s[i + 4], s[i + 5])), make_float2(c1.x, c1.y));
@@ -730,13 +717,41 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           s[i] = a.x; s[i + 1] = a.y; s[i + 2] = b.x; s[i + 3] = b.y;
           s[i + 4] = c.x; s[i + 5] = c.y; s[i + 6] = d.x; s[i + 7] = d.y;
         }
-        if ((tid & 127) == 0) TR(n, 3);
-        noff = -fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * kLog2e;
-        // Pass 2: e = 2^(log2e * w - off) in place, row sum
-        const float2 mulv = make_float2(kLog2e, kLog2e), noffv = make_float2(noff, noff);
+      }
+      // Each half row is exponentiated against its OWN maximum; the halves then exchange (shift, sum,
+      // entropy sum) once and rescale - one barrier per item instead of two.  With top the shift of the
+      // whole row (the larger of the two: max(max(a, eps), max(b, eps)) = max(max(a, b), eps)) and
+      // c = 2^(shift_h - top) <= 1:   e_i = c e'_i,   sum e_i log2 e_i = c (sum e'_i u'_i + log2(c) sum e'_i).
+      const float hmax = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+      float my_off, part_sum, part_ent = 0.f;  // my_off: this half's shift in log2 units
+      if (right) {
+        // x = sm_scale * round(S) / (cr + eps), clamp on the maximum from below
+        const float row_scale = g.sm_scale / ((it.first ? 1.0f : vec[row]) + kEps);
+        const float mul = row_scale * kLog2e;
+        my_off = fmaxf(round_through<T>(hmax) * row_scale, kEps) * kLog2e;
+        // Pass 2: e' = 2^(mul * round(S) - off) in place, sum, sum of e' * log2(e')
+        const float2 mulv = make_float2(mul, mul), noffv = make_float2(-my_off, -my_off);
+        float2 sum_a = make_float2(0.f, 0.f), sum_b = sum_a, ent_a = sum_a, ent_b = sum_a;
+#pragma unroll
+        for (int i = 0; i < kMine; i += 4) {
+          const float2 ua = fma2(round2<T>(make_float2(s[i], s[i + 1])), mulv, noffv);
+          const float2 ub = fma2(round2<T>(make_float2(s[i + 2], s[i + 3])), mulv, noffv);
+          const float2 ea = make_float2(ex2(ua.x), ex2(ua.y)), eb = make_float2(ex2(ub.x), ex2(ub.y));
+          sum_a = add2(sum_a, ea);
+          sum_b = add2(sum_b, eb);
+          ent_a = fma2(ea, ua, ent_a);
+          ent_b = fma2(eb, ub, ent_b);
+          s[i] = ea.x; s[i + 1] = ea.y; s[i + 2] = eb.x; s[i + 3] = eb.y;
+        }
+        part_sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
+        part_ent = (ent_a.x + ent_a.y) + (ent_b.x + ent_b.y);
+      } else {
+        my_off = hmax * kLog2e;
+        // Pass 2: e' = 2^(log2e * w - off) in place, sum
+        const float2 mulv = make_float2(kLog2e, kLog2e), noffv = make_float2(-my_off, -my_off);
         float2 sum_a = make_float2(0.f, 0.f), sum_b = sum_a;
 #pragma unroll
-        for (int i = 0; i < kCols; i += 4) {
+        for (int i = 0; i < kMine; i += 4) {
           const float2 ua = fma2(make_float2(s[i], s[i + 1]), mulv, noffv);
           const float2 ub = fma2(make_float2(s[i + 2], s[i + 3]), mulv, noffv);
           const float2 ea = make_float2(ex2(ua.x), ex2(ua.y)), eb = make_float2(ex2(ub.x), ex2(ub.y));
@@ -744,38 +759,65 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           sum_b = add2(sum_b, eb);
           s[i] = ea.x; s[i + 1] = ea.y; s[i + 2] = eb.x; s[i + 3] = eb.y;
         }
-        row_sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
+        part_sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
+      }
+      if ((tid & 255) == 0) TR(n, 3);
+      xch[grp * 128 + row] = my_off;
+      xch[256 + grp * 128 + row] = part_sum;
+      xch[512 + grp * 128 + row] = part_ent;
+      // the exchange; also the one place where the 256 threads agree to leave (a thread that went on or
+      // left alone would strand the others at the barrier)
+      if (named_barrier_or(kSoftmaxBarrier + (n & 1), 256, !ok)) {
+        if (!ok) give_up(401);
+        break;
+      }
+      // (both halves evaluate the same expressions on the same six numbers, so they get the same bits)
+      const float off0 = xch[row], off1 = xch[128 + row];
+      const float top = fmaxf(off0, off1);
+      const float c0 = ex2(off0 - top), c1 = ex2(off1 - top);
+      const float s0 = xch[256 + row], s1 = xch[384 + row];
+      const float row_sum = c0 * s0 + c1 * s1;
+      float inv;
+      if (right) {
+        const float row_ent = c0 * (xch[512 + row] + (off0 - top) * s0) + c1 * (xch[640 + row] + (off1 - top) * s1);
+        const float denom = row_sum + kEps;
+        inv = __frcp_rn(denom);
+        // cl of the row for the epilogue group: sum_i r_i ln r_i with r_i = e_i / denom and ln e_i = ln2 * u_i.
+        // The 4-deep ring cannot be overrun: the first contraction of item n+4 needs the accumulator buffer
+        // of item n+1 back from the epilogue, which takes the items in order.
+        if (grp == 0)
+          reinterpret_cast<float*>(base_ptr + kOffStats)[(n & 3) * 128 + row] = (kLn2 * row_ent - __logf(denom) * row_sum) * inv;
+        // al = sm_scale * (P k): the scale is a power of two (D = 64), so it can ride on P exactly; the
+        // stage with V keeps P unscaled (y = P v) and scales the al half in the epilogue
+        if (it.kind == kStageRight) inv *= g.sm_scale;
+      } else {
         inv = __frcp_rn(row_sum);
       }
-      // cl of the row for the epilogue group.  The 4-deep ring cannot be overrun: the first contraction
-      // of item n+4 needs the S buffer of item n+1, which its second contraction frees, which needs O
-      // free, i.e. the epilogue of item n past its read of this entry.
-      reinterpret_cast<float*>(base_ptr + kOffStats)[(n & 3) * 128 + row] = stat;
-      mbar_arrive(bar(kBarStat + (n & 3)));
+      inv *= grp == 0 ? c0 : c1;  // this half's exponentials were taken against its own shift
+      if (grp == 0) mbar_arrive(bar(kBarStat + (n & 3)));
+      if ((tid & 255) == 0) TR(n, 8);
 
       const float2 invv = make_float2(inv, inv);
-      if ((tid & 127) == 0) TR(n, 8);
       if (it.kind != kStageLeft) {
-        // Pass 3: P = round(e / sum) into the group's P buffer in tensor memory: A operand of the second
-        // contraction.  (The buffer is free once the second contraction of the group's previous item has
-        // completed - long ago, as a rule.)
-        if (!mbar_wait_abortable(bar(kBarPEmpty + pb), ((uint32_t)(n >> 1) & 1u) ^ 1u, abort_flag)) { give_up(404); break; }
+        // Pass 3: P = round(e / sum) into the item's P buffer in tensor memory: A operand of the second
+        // contraction.  (The buffer is free once the second contraction of item n - 2 has completed - long
+        // ago, as a rule.  A wait that runs out is reported and noticed at the next item's first barrier.)
+        if (!mbar_wait_abortable(bar(kBarPEmpty + pb), ((uint32_t)(n >> 1) & 1u) ^ 1u, abort_flag)) give_up(404);
         tc_fence_after();
         const uint32_t tmem_p = tmem + lane_base + kTmemP + pb * 64;
-        uint32_t pk[32];
+        uint32_t pk[kMine / 2];
 #pragma unroll
-        for (int c = 0; c < kCols / 64; ++c) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float2 r = mul2(make_float2(s[64 * c + 2 * i], s[64 * c + 2 * i + 1]), invv);
-            pk[i] = pack2<T>(r.x, r.y);
-          }
-          tmem_st32(tmem_p + 32 * (h0 + c), pk);
+        for (int i = 0; i < kMine / 2; ++i) {
+          const float2 r = mul2(make_float2(s[2 * i], s[2 * i + 1]), invv);
+          pk[i] = pack2<T>(r.x, r.y);
         }
-        if (per > 1) {
+        if (per == 1) {
+          tmem_st32(tmem_p + 32 * grp, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
+        } else {
+          tmem_st16(tmem_p + 32 * h0 + 16 * grp, *reinterpret_cast<uint32_t(*)[16]>(&pk[0]));
 #pragma unroll
-          for (int i = 0; i < 32; ++i) pk[i] = 0u;
-          tmem_st32(tmem_p + 32 * (1 - h0), pk);
+          for (int i = 0; i < 16; ++i) pk[i] = 0u;
+          tmem_st16(tmem_p + 32 * (1 - h0) + 16 * grp, *reinterpret_cast<uint32_t(*)[16]>(&pk[0]));
         }
         tmem_wait_st();
         tc_fence_before();
@@ -785,11 +827,14 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         // has completed its second contraction.
         if (it.p_dist > 0) {
           const int m = n - it.p_dist;
-          if (!mbar_wait_abortable(bar(kBarInEmpty + m % kSlots), (uint32_t)(m / kSlots) & 1u, abort_flag)) { give_up(403); break; }
+          if (!mbar_wait_abortable(bar(kBarInEmpty + m % kSlots), (uint32_t)(m / kSlots) & 1u, abort_flag)) give_up(403);
         }
         const uint32_t sP = base + kOffPreg;
+        // 16-byte groups of this thread's columns: atom (64 columns) and group within it
+        const uint32_t atom = per > 1 ? (uint32_t)h0 : (uint32_t)grp;
+        const uint32_t g0 = per > 1 ? 4u * (uint32_t)grp : 0u;
 #pragma unroll
-        for (int c8 = 0; c8 < kCols / 8; ++c8) {
+        for (int c8 = 0; c8 < kMine / 8; ++c8) {
           uint32_t hi[4], lo[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -798,14 +843,14 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
             const float2 d = sub2(r, widen2<T>(hi[i]));
             lo[i] = pack2<T>(d.x, d.y);
           }
-          const uint32_t off = (uint32_t)(h0 + (c8 >> 3)) * kTileBytes + swz(row, c8 & 7);
+          const uint32_t off = atom * kTileBytes + swz(row, g0 + c8);
           st_shared_v4(sP + off, hi[0], hi[1], hi[2], hi[3]);
           st_shared_v4(sP + 2 * kTileBytes + off, lo[0], lo[1], lo[2], lo[3]);
         }
         if (per > 1) {
 #pragma unroll
-          for (int c8 = 0; c8 < 8; ++c8) {
-            const uint32_t off = (uint32_t)(1 - h0) * kTileBytes + swz(row, c8);
+          for (int c8 = 0; c8 < 4; ++c8) {
+            const uint32_t off = (uint32_t)(1 - h0) * kTileBytes + swz(row, g0 + c8);
             st_shared_v4(sP + off, 0u, 0u, 0u, 0u);
             st_shared_v4(sP + 2 * kTileBytes + off, 0u, 0u, 0u, 0u);
           }
@@ -813,7 +858,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         fence_async_smem();
       }
       mbar_arrive(bar(kBarPFull + pb));
-      if ((tid & 127) == 0) TR(n, 9);
+      if ((tid & 255) == 0) TR(n, 9);
     }
   }
 
