@@ -119,7 +119,7 @@ enum {
 };
 static_assert(kNumBars <= kNumBarsConst, "barrier count");
 constexpr int kEpilogueBarrier = 1;  // named barrier of the 128 epilogue threads
-constexpr int kSoftmaxBarrier = 3;   // named barriers of the 256 softmax threads: this one and the next
+constexpr int kSoftmaxBarrier = 3;   // named barriers 3..6: one per pair of softmax warps that share rows
 
 struct FusedArgs {
   int stage_begin, stage_end;  // stages [begin, end) of the 2T stages run in this launch
@@ -685,7 +685,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       if (grp == 0) mbar_arrive(bar(kBarStat + (n & 3)));
       tc_fence_before();
       mbar_arrive(bar(kBarPFull + pb));
-      if (named_barrier_or(kSoftmaxBarrier, 256, !ok)) break;
+      if (named_barrier_or(kSoftmaxBarrier + (warp & 3), 64, !ok)) break;
       continue;
 #endif
       // Pass 1: maximum of this half row.  Right-factor stages: of S itself (rounding is monotonic, so the
@@ -765,9 +765,10 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       xch[grp * 128 + row] = my_off;
       xch[256 + grp * 128 + row] = part_sum;
       xch[512 + grp * 128 + row] = part_ent;
-      // the exchange; also the one place where the 256 threads agree to leave (a thread that went on or
-      // left alone would strand the others at the barrier)
-      if (named_barrier_or(kSoftmaxBarrier + (n & 1), 256, !ok)) {
+      // the exchange, between the two warps that share the rows (they also share a scheduler, so they get
+      // here together); also the one place where the pair agrees to leave (a thread that went on or left
+      // alone would strand its partners at the barrier)
+      if (named_barrier_or(kSoftmaxBarrier + (warp & 3), 64, !ok)) {
         if (!ok) give_up(401);
         break;
       }
@@ -777,24 +778,28 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       const float c0 = ex2(off0 - top), c1 = ex2(off1 - top);
       const float s0 = xch[256 + row], s1 = xch[384 + row];
       const float row_sum = c0 * s0 + c1 * s1;
-      float inv;
-      if (right) {
-        const float row_ent = c0 * (xch[512 + row] + (off0 - top) * s0) + c1 * (xch[640 + row] + (off1 - top) * s1);
-        const float denom = row_sum + kEps;
-        inv = __frcp_rn(denom);
-        // cl of the row for the epilogue group: sum_i r_i ln r_i with r_i = e_i / denom and ln e_i = ln2 * u_i.
-        // The 4-deep ring cannot be overrun: the first contraction of item n+4 needs the accumulator buffer
-        // of item n+1 back from the epilogue, which takes the items in order.
-        if (grp == 0)
-          reinterpret_cast<float*>(base_ptr + kOffStats)[(n & 3) * 128 + row] = (kLn2 * row_ent - __logf(denom) * row_sum) * inv;
-        // al = sm_scale * (P k): the scale is a power of two (D = 64), so it can ride on P exactly; the
-        // stage with V keeps P unscaled (y = P v) and scales the al half in the epilogue
-        if (it.kind == kStageRight) inv *= g.sm_scale;
-      } else {
-        inv = __frcp_rn(row_sum);
-      }
-      inv *= grp == 0 ? c0 : c1;  // this half's exponentials were taken against its own shift
-      if (grp == 0) mbar_arrive(bar(kBarStat + (n & 3)));
+      // 1 / sum by the approximate reciprocal (1 ulp; the quotient is rounded to 16 bits right after) - the
+      // exact one is a long dependent sequence on the path of every item
+      const float denom = right ? row_sum + kEps : row_sum;
+      float rden;
+      asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rden) : "f"(denom));
+      // this half's exponentials were taken against its own shift.  al = sm_scale * (P k): the scale is a
+      // power of two (D = 64), so it can ride on P exactly; the stage with V keeps P unscaled (y = P v)
+      // and scales the al half in the epilogue
+      float inv = rden * (grp == 0 ? c0 : c1);
+      if (it.kind == kStageRight) inv *= g.sm_scale;
+      // cl of the row for the epilogue group, off the path to P: sum_i r_i ln r_i with r_i = e_i / denom and
+      // ln e_i = ln2 * u_i.  The 4-deep ring cannot be overrun: the first contraction of item n+4 needs the
+      // accumulator buffer of item n+1 back from the epilogue, which takes the items in order.
+      auto post_stat = [&]() {
+        if (grp == 0) {
+          if (right) {
+            const float row_ent = c0 * (xch[512 + row] + (off0 - top) * s0) + c1 * (xch[640 + row] + (off1 - top) * s1);
+            reinterpret_cast<float*>(base_ptr + kOffStats)[(n & 3) * 128 + row] = (kLn2 * row_ent - __logf(denom) * row_sum) * rden;
+          }
+          mbar_arrive(bar(kBarStat + (n & 3)));
+        }
+      };
       if ((tid & 255) == 0) TR(n, 8);
 
       const float2 invv = make_float2(inv, inv);
@@ -858,6 +863,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         fence_async_smem();
       }
       mbar_arrive(bar(kBarPFull + pb));
+      post_stat();
       if ((tid & 255) == 0) TR(n, 9);
     }
   }
