@@ -7,7 +7,10 @@ Workload (the configuration the headline metric is quoted on): one bf16 MonarchA
 call with batch 1, 16 heads, N = 16384 tokens as 128 blocks of 128, head width 64, two
 alternating iterations, q/k/v ~ N(0,1)/sqrt(64) from a fixed seed, no mask.  A "step" is
 one such call.  With N > 1 GPUs every rank runs the same per-GPU workload on its own
-inputs (independent (batch, head) units, no data-path collective): weak scaling.
+inputs (independent (batch, head) units, no data-path collective): weak scaling.  With
+``--scaling strong`` the 16 heads of ONE call are split across the ranks instead (16 / 8 / 4 / 2
+heads per GPU), and the per-head checksums of the shards are gathered on rank 0 and compared
+with the unsharded call.
 
 Prints ONE JSON line on rank 0.
 """
@@ -159,34 +162,59 @@ def max_over_ranks(x, world, device):
 # ---------------------------------------------------------------------------------------------
 # CPU oracle timing (the reference's algorithm restated on the host; see oracle/)
 # ---------------------------------------------------------------------------------------------
+def reference_package():
+    """The reference's own ``ma`` package from oracle/_ref (placed there by oracle/make_ref.py, git-ignored),
+    or None.  Used for timing only, never by the product."""
+    ref_dir = os.path.join(ROOT, "oracle", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "ma")):
+        return None
+    if ref_dir not in sys.path:
+        sys.path.insert(0, ref_dir)
+    try:
+        import ma.monarch_attention as mod  # noqa: PLC0415
+        return mod
+    except Exception:
+        return None
+
+
 def time_oracle(heads, reps, warm):
-    from oracle.monarch_oracle import monarch_attention_oracle
+    """CPU timing of the reference's eager implementation on `heads` heads of the workload: the reference's
+    own ma_torch when oracle/_ref holds it (kind "reference"), else the oracle port (kind "port")."""
     w = WORKLOAD
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     q, k, v = make_inputs(0)
     q, k, v = q[:, :heads], k[:, :heads], v[:, :heads]
-    for _ in range(warm):
-        monarch_attention_oracle(q, k, v, None, w["T"], w["B"], False)
-    times = []
-    for _ in range(reps):
-        t0 = time.perf_counter()
-        monarch_attention_oracle(q, k, v, None, w["T"], w["B"], False)
-        times.append(time.perf_counter() - t0)
-    return times, cores
+    mod = reference_package()
+    if mod is not None:
+        ref = mod.MonarchAttention(w["B"], w["T"], "post", impl="torch")
+        fn, kind = (lambda: ref(q, k, v)), "reference"
+    else:
+        from oracle.monarch_oracle import monarch_attention_oracle
+        fn, kind = (lambda: monarch_attention_oracle(q, k, v, None, w["T"], w["B"], False)), "port"
+    with torch.no_grad():
+        for _ in range(warm):
+            fn()
+        times = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            fn()
+            times.append(time.perf_counter() - t0)
+    return times, cores, kind
 
 
 def run_reference(args, rank, world):
-    """Reference arm: the reference's CPU algorithm (oracle port) on the host cores, rank 0 only."""
+    """Reference arm: the reference's CPU implementation of the path on the host cores (its own ma_torch
+    from oracle/_ref when present, else the oracle port), rank 0 only."""
     if rank != 0:
         return
     w = WORKLOAD
     # probe the cost of one head, then size the per-step sample so the run stays within ~150 s
-    probe, cores = time_oracle(1, 1, 1)
+    probe, cores, kind = time_oracle(1, 1, 1)
     per_head = probe[0]
     seconds_per_step = 150.0 / max(args.steps + args.warmup, 1)
     heads = int(max(1, min(w["H"], seconds_per_step / per_head)))
-    times, cores = time_oracle(heads, args.steps, args.warmup)
+    times, cores, kind = time_oracle(heads, args.steps, args.warmup)
     total = sum(times)
     # tokens/s of the full 16-head op = E*N / (time for H heads); a sample of `heads` heads scales linearly
     step_s = total / args.steps
@@ -197,7 +225,7 @@ def run_reference(args, rank, world):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * step_s * w["H"] / heads,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": w["name"], **{k: w[k] for k in ("E", "H", "N", "D", "B", "T")}},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -205,88 +233,148 @@ def run_reference(args, rank, world):
 
 
 # ---------------------------------------------------------------------------------------------
-# ViT-B/16 forward with MonarchAttention in every layer (second half of the headline metric)
+# Context measurements: the three caller models, the reference's own GPU paths
 # ---------------------------------------------------------------------------------------------
-def build_vit_b(attn_factory, dtype, device):
-    """Plain-PyTorch ViT-B/16 (224x224x3 input, 196 patches + CLS, 12 pre-LN layers, hidden 768,
-    12 heads of 64, MLP 3072 with GELU), trunc-normal(0.02) random weights.  The attention call site is
-    the reference adapter's: q, k, v as permuted (E, H, N, D) views of the projection outputs,
-    ``attn_module(q, k, v)``, then ``permute(0, 2, 1, 3)`` back (reference: experiments/vit/model.py:73-103)."""
-    import torch.nn as nn
-
-    class Block(nn.Module):
-        def __init__(self):
-            super().__init__()
-            self.ln1, self.ln2 = nn.LayerNorm(768, eps=1e-12), nn.LayerNorm(768, eps=1e-12)
-            self.q, self.k, self.v, self.o = (nn.Linear(768, 768) for _ in range(4))
-            self.fc1, self.fc2 = nn.Linear(768, 3072), nn.Linear(3072, 768)
-            self.attn = attn_factory()
-
-        def forward(self, x):
-            E, N, _ = x.shape
-            hdn = self.ln1(x)
-            q, k, v = (p(hdn).view(E, N, 12, 64).permute(0, 2, 1, 3) for p in (self.q, self.k, self.v))
-            ctx = self.attn(q, k, v).permute(0, 2, 1, 3).contiguous().view(E, N, 768)
-            x = x + self.o(ctx)
-            return x + self.fc2(torch.nn.functional.gelu(self.fc1(self.ln2(x))))
-
-    class ViT(nn.Module):
-        def __init__(self):
-            super().__init__()
-            self.patch = nn.Conv2d(3, 768, 16, 16)
-            self.cls = nn.Parameter(torch.zeros(1, 1, 768))
-            self.pos = nn.Parameter(torch.zeros(1, 197, 768))
-            self.blocks = nn.ModuleList(Block() for _ in range(12))
-            self.ln = nn.LayerNorm(768, eps=1e-12)
-            self.head = nn.Linear(768, 1000)
-
-        def forward(self, img):
-            x = self.patch(img).flatten(2).transpose(1, 2)
-            x = torch.cat((self.cls.expand(x.shape[0], -1, -1), x), dim=1) + self.pos
-            for b in self.blocks:
-                x = b(x)
-            return self.head(self.ln(x)[:, 0])
-
-    torch.manual_seed(0)
-    model = ViT()
-    for p_ in model.parameters():
-        if p_.dim() > 1:
-            torch.nn.init.trunc_normal_(p_, std=0.02)
-    return model.to(device=device, dtype=dtype).eval()
+def _time_model(model, inputs, steps, warmup):
+    with torch.no_grad():
+        for _ in range(warmup):
+            out = model(*inputs)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            out = model(*inputs)
+        e1.record()
+        torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps, bool(torch.isfinite(out.float()).all())
 
 
-def time_vit(device, steps=10, warmup=3, batch=64):
-    """img/s of the ViT-B forward, bf16, batch 64, block size 15, one iteration, front padding; and the
-    same model with dense SDPA as context."""
+def time_models(device, rank, world, steps=5, warmup=2):
+    """Forward throughput of the three caller models (monarch_attention_b200/models.py: plain PyTorch, random
+    weights, seeded synthetic inputs) with this library's attention and with dense SDPA, bf16.  The batch of
+    each configuration is split across the ranks (64 / 32 / 16 / 8 per GPU ...); the per-rank times are
+    gathered on rank 0 with one collective and the slowest rank sets the aggregate rate."""
     from monarch_attention_b200 import MonarchAttention
+    from monarch_attention_b200.models import DenseAttention, build_dit_xl2, build_roberta_base, build_vit_b16
+    from monarch_attention_b200.sharding import gather_to_rank0, unit_range
 
-    class Dense(torch.nn.Module):
-        def forward(self, q, k, v):
-            return torch.nn.functional.scaled_dot_product_attention(q, k, v)
-
-    def monarch():
-        m = MonarchAttention(15, 1, "pre")
-        m.token_major_output = True
-        return m
+    def monarch(B, T, pad):
+        def make():
+            m = MonarchAttention(B, T, pad)
+            m.token_major_output = True
+            return m
+        return make
 
     g = torch.Generator(device="cpu").manual_seed(0)
-    img = torch.rand(batch, 3, 224, 224, generator=g).to(torch.bfloat16).to(device)
+
+    def vit_inputs(n):
+        return (torch.rand(n, 3, 224, 224, generator=g).to(torch.bfloat16).to(device),)
+
+    def roberta_inputs(n):
+        ids = torch.randint(3, 50265, (n, 512), generator=g)
+        mask = torch.ones(n, 512, dtype=torch.long)
+        for e in range(0, n, 4):  # a quarter of the sequences right-padded to a random length in [128, 512]
+            ln = int(torch.randint(128, 513, (1,), generator=g))
+            mask[e, ln:] = 0
+            ids[e, ln:] = 1
+        return ids.to(device), mask.to(device)
+
+    def dit_inputs(n):
+        return (torch.randn(n, 4, 64, 64, generator=g).to(torch.bfloat16).to(device),
+                torch.randint(0, 1000, (n,), generator=g).to(device), torch.randint(0, 1000, (n,), generator=g).to(device))
+
+    configs = [
+        ("vit_b16_bf16_batch64_b15_T1", build_vit_b16, vit_inputs, 64, monarch(15, 1, "pre"), "img_per_s"),
+        ("roberta_base_bf16_batch32_n512_b32_T1_mask", build_roberta_base, roberta_inputs, 32, monarch(32, 1, "post"), "seq_per_s"),
+        ("dit_xl2_bf16_batch64_n1024_d72_b32_T2", build_dit_xl2, dit_inputs, 64, monarch(32, 2, "pre"), "img_per_s"),
+    ]
     out = {}
-    for name, factory in (("monarch_b200", monarch), ("dense_sdpa", Dense)):
-        model = build_vit_b(factory, torch.bfloat16, device)
-        with torch.no_grad():
-            for _ in range(warmup):
-                model(img)
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(steps):
-                logits = model(img)
-            e1.record()
-            torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / steps
-        out[name] = {"img_per_s": batch / (ms * 1e-3), "ms_per_forward": ms, "finite": bool(torch.isfinite(logits).all())}
+    for name, build, make_in, batch, factory, unit in configs:
+        lo, hi = unit_range(batch, rank, world)
+        res = {}
+        if hi > lo:
+            inputs = make_in(hi - lo)
+            for label, fac in (("monarch_b200", factory), ("dense_sdpa", DenseAttention)):
+                model = build(fac, torch.bfloat16, device)
+                ms, finite = _time_model(model, inputs, steps, warmup)
+                res[label] = (ms, finite)
+                del model
+            torch.cuda.empty_cache()
+        gathered = gather_to_rank0({"n": hi - lo, "res": res})
+        if rank == 0:
+            entry = {"batch": batch, "per_rank_batch": [x["n"] for x in gathered]}
+            for label in ("monarch_b200", "dense_sdpa"):
+                times = [x["res"][label][0] for x in gathered if x["res"]]
+                entry[label] = {unit: batch / (max(times) * 1e-3), "ms_per_forward": max(times),
+                                "finite": all(x["res"][label][1] for x in gathered if x["res"])}
+            out[name] = entry
     return out
+
+
+def time_reference_gpu(q, k, v, T, B, reps=5):
+    """The reference's own module on this GPU: eager PyTorch (impl="torch") and its Triton kernels
+    (impl="triton"), from oracle/_ref when that directory travelled with the tree."""
+    mod = reference_package()
+    if mod is None:
+        return {"unavailable": "oracle/_ref is not present (run oracle/make_ref.py where the reference is checked out)"}
+    out = {}
+    for impl in ("torch", "triton"):
+        try:
+            m = mod.MonarchAttention(B, T, "post", impl=impl)
+            with torch.no_grad():
+                for _ in range(2):
+                    res = m(q, k, v)
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(reps):
+                    res = m(q, k, v)
+                e1.record()
+                torch.cuda.synchronize()
+            out[f"reference_{impl}_gpu_ms"] = e0.elapsed_time(e1) / reps
+            out[f"reference_{impl}_gpu_finite"] = bool(torch.isfinite(res.float()).all())
+        except Exception as exc:  # e.g. the Triton kernels do not compile with the installed Triton
+            out[f"reference_{impl}_gpu_ms"] = None
+            out[f"reference_{impl}_gpu_unavailable"] = (str(exc).strip().splitlines() or [repr(exc)])[0][:160]
+    return out
+
+
+def fused_kernel_dram_traffic():
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of the fused kernel on the headline workload,
+    as recorded in the committed ncu summary (a profiler cannot run inside this script)."""
+    import re
+    try:
+        text = open(os.path.join(ROOT, "profiles", "fused_kernel_c3_n16384_bf16.md")).read()
+        m = re.search(r"dram_traffic_bytes_per_launch\s*=\s*([0-9.eE+]+)", text)
+        return float(m.group(1)) if m else None
+    except OSError:
+        return None
+
+
+def bind_to_gpu_numa_node(local):
+    """Run this rank's host threads (and therefore first-touch its pinned staging buffers) on the NUMA node the
+    GPU hangs off.  Host placement only; nothing about the GPU is changed."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        bus = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(local)).busId
+        bus = (bus.decode() if isinstance(bus, bytes) else bus).lower()
+        if len(bus.split(":")[0]) == 8:
+            bus = bus[4:]
+        node = int(open(f"/sys/bus/pci/devices/{bus}/numa_node").read())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return {"numa_node": node, "cpus": len(cpus)}
+    except Exception:
+        pass
+    return None
 
 
 # ---------------------------------------------------------------------------------------------
@@ -295,14 +383,21 @@ def time_vit(device, steps=10, warmup=3, batch=64):
 def run_ours(args, rank, world, local):
     from monarch_attention_b200 import MonarchAttention, _cabi
     from monarch_attention_b200.monarch_attention import make_problem
+    from monarch_attention_b200.sharding import gather_to_rank0, shard_heads
 
     lib = _cabi.load()
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
+    numa = bind_to_gpu_numa_node(local)
     w = WORKLOAD
     warmup = max(args.warmup, 3)
+    strong = args.scaling == "strong"
     mod = MonarchAttention(w["B"], w["T"], "post")
-    sets = [make_inputs(1000 * rank + i, dev) for i in range(N_INPUT_SETS)]
+    if strong:
+        # ONE call's 16 heads split across the ranks: every rank draws the same full inputs and keeps its slice
+        sets = [tuple(t.contiguous() for t in shard_heads(*make_inputs(i, dev), rank, world)) for i in range(N_INPUT_SETS)]
+    else:
+        sets = [make_inputs(1000 * rank + i, dev) for i in range(N_INPUT_SETS)]
     outs = [torch.empty_like(s[2]) for s in sets]
 
     def step(i):
@@ -327,8 +422,20 @@ def run_ours(args, rank, world, local):
     barrier(world)
     ms_total = max_over_ranks(ev0.elapsed_time(ev1), world, dev)
     ms_step = ms_total / args.steps
-    tokens_per_step = w["E"] * w["N"] * world
+    tokens_per_step = w["E"] * w["N"] * (1 if strong else world)
     value = tokens_per_step / (ms_step * 1e-3)
+
+    shard_check = None
+    if strong:
+        # per-head checksums of the sharded call, gathered on rank 0 and compared with the unsharded call
+        o = step(0).float()
+        mine = torch.stack([o.sum(dim=(-1, -2)).flatten(), (o * o).sum(dim=(-1, -2)).flatten()]).cpu()
+        parts = gather_to_rank0(mine)
+        if rank == 0:
+            full = MonarchAttention(w["B"], w["T"], "post")(*make_inputs(0, dev)).float()
+            want = torch.stack([full.sum(dim=(-1, -2)).flatten(), (full * full).sum(dim=(-1, -2)).flatten()]).cpu()
+            got = torch.cat(parts, dim=1)
+            shard_check = "bitwise" if torch.equal(got, want) else f"max diff {float((got - want).abs().max()):.3e}"
 
     # ---- end to end: pinned host inputs -> device -> op -> pinned host result, every step -------------
     e2e_steps = max(3, min(args.steps, 20))
@@ -358,6 +465,16 @@ def run_ours(args, rank, world, local):
     d2h = hout.numel() * hout.element_size()
     sampler.stop()
 
+    # ---- the caller models, batch split across the ranks (one gather per model) ---------------------
+    context = {}
+    if not args.no_models:
+        try:
+            models = time_models(dev, rank, world)
+            if rank == 0:
+                context.update(models)
+        except Exception as exc:
+            context["models_error"] = str(exc)[:200]
+
     if rank != 0:
         return
 
@@ -386,20 +503,25 @@ def run_ours(args, rank, world, local):
             for i in range(n_stage):
                 acc[i] += buf[i] / reps
     _cabi.raise_for_status(lib.ma_b200_device_status(ws.data_ptr(), stream))
+    _cabi.raise_for_status(lib.ma_b200_poll_device_status(local))
     flops, nbytes, stage_flops = work_model()
+    if strong:
+        flops, nbytes = flops / world, nbytes / world  # this rank's share; the roofline below is per GPU
     names = ["right", "left", "right_with_v", "output"]
-    stages = [{"stage": n, "ms": acc[i], "tflops": stage_flops[n] / (acc[i] * 1e-3) / 1e12} for i, n in enumerate(names)]
+    stages = [{"stage": n, "ms": acc[i], "tflops": stage_flops[n] / (world if strong else 1) / (acc[i] * 1e-3) / 1e12}
+              for i, n in enumerate(names)]
     peaks = measured_peaks()
     t_tensor = flops / (peaks["bf16_tflops"] * 1e12)
     t_hbm = nbytes / (peaks["hbm_gbs"] * 1e9)
     achieved_tflops = flops / (ms_step * 1e-3) / 1e12
+    fused = L_auto.kernel == _cabi.KERNEL_TCGEN05
     roofline = {
         "bound": "tensor" if t_tensor >= t_hbm else "hbm",
         "achieved": achieved_tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
         "frac": achieved_tflops / peaks["bf16_tflops"],
-        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the fused kernel on this workload,
-        # from an `ncu --set full` capture (profiles/fused_kernel_c3_n16384_bf16.md); not measured live
-        "traffic": 245.8e6 if L_auto.kernel == _cabi.KERNEL_TCGEN05 else None,
+        # per launch of the fused kernel on this workload, from the committed `ncu` summary under profiles/
+        "traffic": fused_kernel_dram_traffic() if fused and not strong else None,
+        "algorithmic_bytes": nbytes,
         "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
         "scope": "whole op = one fused launch per step; algorithmic FLOPs / ms_per_step; `stages` = the same "
                  "kernel launched once per stage",
@@ -407,8 +529,7 @@ def run_ours(args, rank, world, local):
         "stages": stages,
     }
 
-    # ---- context: dense SDPA on the same GPU, same q, k, v ------------------------------------------
-    context = {}
+    # ---- context: dense SDPA and the reference's own GPU paths on the same GPU, same q, k, v --------
     try:
         import torch.nn.functional as F
         for _ in range(2):
@@ -424,42 +545,42 @@ def run_ours(args, rank, world, local):
     except Exception as exc:  # context only
         context["dense_sdpa_ms"] = None
         context["dense_sdpa_error"] = str(exc)[:100]
+    if not args.no_reference_gpu:
+        context.update(time_reference_gpu(q, k, v, w["T"], w["B"]))
 
-    # ---- second half of the headline metric: ViT-B/16 forward, img/s -----------------------------------
-    try:
-        context["vit_b16_bf16_batch64_b15_T1"] = time_vit(dev)
-    except Exception as exc:
-        context["vit_b16_error"] = str(exc)[:200]
-
-    # ---- CPU baseline: the oracle port on the host cores, bounded sample ----------------------------
+    # ---- CPU baseline: the reference's eager path on the host cores, bounded sample -----------------
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
-        probe, cores = time_oracle(1, 1, 1)
+        probe, cores, kind = time_oracle(1, 1, 1)
         heads = int(max(1, min(w["H"], 5.0 / probe[0])))
-        times, cores = time_oracle(heads, 3, 0)
+        times, cores, kind = time_oracle(heads, 3, 0)
         step_s = statistics.median(times) * w["H"] / heads
-        cpu_baseline = {"value": w["E"] * w["N"] / step_s, "unit": UNIT, "cores": cores, "kind": "port",
+        cpu_baseline = {"value": w["E"] * w["N"] / step_s, "unit": UNIT, "cores": cores, "kind": kind,
                         "sample": f"median of 3 passes over {heads} of {w['H']} heads, scaled by {w['H']}/{heads}",
                         "ms_per_step": 1e3 * step_s}
 
+    heads_per_gpu = w["H"] // world if strong else w["H"]
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
-        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic",
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if strong else "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": w["name"], **{k_: w[k_] for k_ in ("E", "H", "N", "D", "B", "T")},
-                   "per_gpu_workload": "full (E=1, H=16) on every rank",
-                   "l2": f"{N_INPUT_SETS} rotating input sets ({N_INPUT_SETS * 3 * 33.5:.0f} MB) > 126 MB L2",
+                   "per_gpu_workload": f"{heads_per_gpu} of the 16 heads per rank" if strong else "full (E=1, H=16) on every rank",
+                   "l2": f"{N_INPUT_SETS} rotating input sets ({N_INPUT_SETS * 3 * 33.5 / (world if strong else 1):.0f} MB) > 126 MB L2"
+                         if not strong or world <= 2 else f"{N_INPUT_SETS} rotating input sets; L2 flushed by nothing else (inputs of a rank are {N_INPUT_SETS * 3 * 33.5 / world:.0f} MB)",
                    "kernel": _cabi.KERNEL_NAMES[L_auto.kernel]},
         "clocks": sampler.summary(),
         "e2e": {"value": tokens_per_step / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps, "host_placement": numa,
                 "api": "monarch_attention_b200_host: pinned host q, k, v in, pinned host result out, "
                        f"{args.e2e_heads_per_chunk} heads per chunk"},
-        "gpu_launches": args.steps * (1 if L_auto.kernel == _cabi.KERNEL_TCGEN05 else n_stage),
+        "gpu_launches": args.steps * (1 if fused else n_stage),
         "roofline": roofline,
         "cpu_baseline": cpu_baseline,
         "context": context,
     }
+    if strong:
+        line["shard_check"] = shard_check
     print(json.dumps(line), flush=True)
 
 
@@ -504,6 +625,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-models", action="store_true", help="skip the ViT / RoBERTa / DiT context measurements")
+    ap.add_argument("--no-reference-gpu", action="store_true", help="skip timing the reference's own GPU paths")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
+                    help="weak: the full 16-head call on every rank; strong: the 16 heads of one call split across ranks")
     ap.add_argument("--e2e-heads-per-chunk", type=int, default=8,
                     help="heads per pipeline chunk of the end-to-end (host memory) measurement")
     ap.add_argument("--layer", default=None, help="E,H,N,D,B,T,pre|post[,mask]: time one layer of that shape instead")

@@ -194,3 +194,18 @@ def test_host_scratch_size_is_host_arithmetic(lib):
     assert b"heads_per_chunk" in lib.ma_b200_host_last_error()
     # null host pointers are refused before any CUDA call
     assert lib.ma_b200_forward_host(C.byref(p), 2, None, 0, None) != 0
+
+
+def test_caller_models_build_and_run_on_cpu():
+    """The plain-PyTorch restatements of the three callers (ViT-B/16, RoBERTa-base encoder, DiT-XL/2) at
+    reduced depth with a dense-attention stand-in: shapes and finiteness (no GPU involved)."""
+    from monarch_attention_b200.models import DenseAttention, build_dit_xl2, build_roberta_base, build_vit_b16
+    torch.manual_seed(0)
+    with torch.no_grad():
+        v = build_vit_b16(DenseAttention, dtype=torch.float32, device="cpu", depth=1)(torch.rand(1, 3, 224, 224))
+        r = build_roberta_base(DenseAttention, dtype=torch.float32, device="cpu", depth=1)(
+            torch.randint(3, 50265, (2, 32)), torch.ones(2, 32, dtype=torch.long))
+        d = build_dit_xl2(DenseAttention, dtype=torch.float32, device="cpu", depth=1)(
+            torch.randn(1, 4, 64, 64), torch.tensor([10]), torch.tensor([7]))
+    assert v.shape == (1, 1000) and r.shape == (2, 32, 768) and d.shape == (1, 8, 64, 64)
+    assert all(torch.isfinite(x).all() for x in (v, r, d))
