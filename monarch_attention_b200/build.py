@@ -24,7 +24,7 @@ NVCC_FLAGS = [
     "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
     "--expt-relaxed-constexpr",
-] + (["-DMA_DIAG"] if os.environ.get("MA_DIAG") else []) + (["-DMA_DIAG", "-DMA_TRACE"] if os.environ.get("MA_TRACE") else [])
+]
 
 
 def find_nvcc() -> str:

@@ -44,7 +44,6 @@
 //   warp 14    MMA issuer 2: the second contraction of item n into O
 // All hand-offs are mbarriers; every wait is bounded and abortable (see ma_sm100.cuh).
 #include <cuda.h>
-#include <stdlib.h>
 
 #include <mutex>
 #include <type_traits>
@@ -57,10 +56,6 @@ namespace ma {
 namespace {
 
 using namespace sm100;
-#ifdef MA_EXP_NOMMA
-#define mma_f16_lo(...) ((void)0)
-#define mma_f16_ts(...) ((void)0)
-#endif
 
 constexpr int kTile = 128;
 constexpr int kHead = 64;
@@ -129,9 +124,6 @@ struct FusedArgs {
   int spin_limit;              // iterations of the planner's dependency wait before it gives up
   int* counters;               // (E*H, 2T) ints, zeroed before the first launch of a call
   int* host_status;            // mapped host word that receives the code of a wait that gave up, or nullptr
-#ifdef MA_TRACE
-  long long* trace;            // [2 CTAs][64 items][16 events] clock64 stamps
-#endif
 };
 
 struct Item {
@@ -165,10 +157,6 @@ __device__ __forceinline__ float2 widen2<__nv_bfloat16>(uint32_t u) {
   return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
 }
 
-__device__ __forceinline__ void red_release_add(int* p, int v) {
-  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
 template <typename T, int PER>  // PER: key blocks (or columns j) per 128-row tile: 1 (block size 128) or 2 (64)
 __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constant__ TcMaps maps, const Geometry g,
                                                             const FusedArgs args) {
@@ -181,12 +169,6 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + kOffBar + 8 * kNumBarsConst + 8);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-#ifdef MA_TRACE
-  const int tr_cta = blockIdx.x == 0 ? 0 : (blockIdx.x == 77 ? 1 : -1);
-#define TR(n_, ev_) do { if (tr_cta >= 0 && args.trace != nullptr && (n_) < 64) args.trace[(tr_cta * 64 + (n_)) * 16 + (ev_)] = clock64(); } while (0)
-#else
-#define TR(n_, ev_) do { } while (0)
-#endif
   constexpr int kFmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
   const int tph = g.N / kTile;  // tiles per head and stage
   constexpr int per = PER;
@@ -269,11 +251,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
   // 256 x 192 + 128 x 80 + 128 x 48 = 65536 = 512 x 128, so the increase can always be granted.
   // (What setmaxnreg redistributes is the allocation the CTA was launched with - threads x registers
   // per thread - not the whole register file: a request beyond that pool blocks for ever.)
-#ifdef MA_EXP_POLITE
-#define ROLE_WAIT(b_, p_) mbar_wait_polite(b_, p_, abort_flag, MA_EXP_POLITE)
-#else
 #define ROLE_WAIT(b_, p_) mbar_wait_abortable(b_, p_, abort_flag)
-#endif
   if (warp >= kPlannerWarp) {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
   if (warp == kPlannerWarp) {
@@ -344,7 +322,6 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           const int kind = d0 & 3, stage = d0 >> 16;
           const bool left = kind == kStageLeft;
           const int ntiles = (kind == kStageRightWithV || kind == kStageOutput) ? 3 : 2;
-          TR(n, 0);
           if (!dok) {  // not yet complete when the batch was prepared: wait here
             const int* ctr = stage > 0 ? args.counters + eh * nst_all + (stage - 1)
                                        : args.counters + (eh - args.group) * nst_all + (nst_all - 1);
@@ -374,7 +351,6 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
             ++oldest;
           }
           if (ok) {
-            TR(n, 1);
             // A left-factor item writes P into the P region: it has to wait for the newest older item that
             // is a left-factor item itself or holds one of those tiles (items complete in order).
             const int p_dist = (left && last_p >= oldest) ? n - last_p : 0;
@@ -432,10 +408,6 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           if (three) tma_load_5d(sV, &maps.y_blk, full, 0, 0, it.tile, it.hs, 0);
           bulk_load(vec, g.cl + ((long long)it.hs * g.B + it.tile * per) * g.M, 512, full);
         }
-        TR(n, 2);
-#ifdef MA_TRACE
-        if (tr_cta >= 0 && args.trace != nullptr && n < 64) args.trace[(tr_cta * 64 + n) * 16 + 15] = it.stage * 1000 + it.eh;
-#endif
       }
       // Drain: make sure every copy this thread started has landed before the CTA may exit.
       for (int m = max(0, issued - kSlots); m < issued; ++m)
@@ -488,7 +460,6 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       for (int n = 0; n < n_items; ++n) {
         const int sb = n % kSBuffers, slot = n % kSlots, pb = n & 1;
         if (!ROLE_WAIT(bar(kBarPFull + pb), (uint32_t)(n >> 1) & 1u)) { give_up(303); break; }
-        TR(n, 10);
         const Item it = read_item(n);
         const int kind = it.kind;
         tc_fence_after();
@@ -524,7 +495,6 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         mma_commit(bar(kBarOFull + sb));
         mma_commit(bar(kBarPEmpty + pb));
         mma_commit(bar(kBarInEmpty + slot));
-        TR(n, 12);
       }
     }
   }
@@ -545,7 +515,6 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         break;
       }
       tc_fence_after();
-      if (tid == 256) TR(n, 13);
       const Item it = read_item(n);
       const float stat = reinterpret_cast<const float*>(base_ptr + kOffStats)[(n & 3) * 128 + row];
       const uint32_t tmem_o = tmem + lane_base + sb * 128;
@@ -598,7 +567,6 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           else st_global_v8(dst + h8 * 16, w);
         }
       };
-#ifndef MA_EXP_NOEPI
       store_row(dst0, tmem_o, scale, it.kind == kStageOutput);
       if (it.kind == kStageRightWithV) {
         store_row(reinterpret_cast<T*>(g.y) + row_y * kHead, tmem_o + kHead, 1.0f, false);
@@ -607,10 +575,8 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         tmem_ld32(tmem_o + kHead, o);
         g.cr[((long long)it.hs * g.M + rin) * g.B + it.tile * per + rblk] = o[0];
       }
-#endif
       tc_fence_before();
       mbar_arrive(bar(kBarSEmpty + sb));  // the accumulator buffer may take the S of item n + 3
-      if (tid == 256) TR(n, 5);
       if (args.wait_deps) {
         // The state tiles this item read (each is written once and read once) are dead: drop their lines
         // from L2 so that they are never written back to HBM and make room at once.  One 128-byte row per
@@ -626,12 +592,10 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         // writer orders its generic-proxy stores before it (a fence on the reading side would make the
         // issuer wait for its own copies in flight, which serialises the loads of consecutive items).
         asm volatile("fence.proxy.async.global;" ::: "memory");
-        if (tid == 256) TR(n, 4);
         // hand the item to the publisher (4-deep ring)
         if (!ROLE_WAIT(bar(kBarPubFree + (n & 3)), ((uint32_t)(n >> 2) & 1u) ^ 1u)) give_up(502);
         mbar_arrive(bar(kBarDone + (n & 3)));
       }
-      if (tid == 256) TR(n, 14);
     }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 192;");
@@ -663,7 +627,6 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       if (ok) it = read_item(n);
       const bool right = it.kind == kStageRight || it.kind == kStageRightWithV;
       tc_fence_after();
-      if ((tid & 255) == 0) TR(n, 6);
       const uint32_t tmem_s = tmem + lane_base + sb * 128;
 
       // This thread's columns of S, read once and kept in registers.
@@ -678,16 +641,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
 #pragma unroll
         for (int i = 0; i < kMine; ++i) s[i] = 0.f;
       }
-      if ((tid & 255) == 0) TR(n, 7);
 
-#ifdef MA_EXP_NOSOFTMAX
-      if (s[0] + s[kMine - 1] == 12345.678f) xch_base[row] = s[0];
-      if (grp == 0) mbar_arrive(bar(kBarStat + (n & 3)));
-      tc_fence_before();
-      mbar_arrive(bar(kBarPFull + pb));
-      if (named_barrier_or(kSoftmaxBarrier + (warp & 3), 64, !ok)) break;
-      continue;
-#endif
       // Pass 1: maximum of this half row.  Right-factor stages: of S itself (rounding is monotonic, so the
       // maximum of the rounded logits is the rounded maximum).  Left-factor / output stages: the logits
       // round(S) - cl[m] are formed in place first.
@@ -761,7 +715,6 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         }
         part_sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
       }
-      if ((tid & 255) == 0) TR(n, 3);
       xch[grp * 128 + row] = my_off;
       xch[256 + grp * 128 + row] = part_sum;
       xch[512 + grp * 128 + row] = part_ent;
@@ -800,7 +753,6 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           mbar_arrive(bar(kBarStat + (n & 3)));
         }
       };
-      if ((tid & 255) == 0) TR(n, 8);
 
       const float2 invv = make_float2(inv, inv);
       if (it.kind != kStageLeft) {
@@ -864,7 +816,6 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       }
       mbar_arrive(bar(kBarPFull + pb));
       post_stat();
-      if ((tid & 255) == 0) TR(n, 9);
     }
   }
 
@@ -959,9 +910,6 @@ cudaError_t launch_fused(const TcPlan* plan, const Geometry& g, int* counters, i
     const int tiles = g.N / kTile;
     int want = 1 + (7 * kTile + tiles - 1) / tiles;  // (want - 1) * tiles >= 7 * 128 items
     if (want < 8) want = 8;
-#ifdef MA_GROUP
-    want = MA_GROUP;
-#endif
     a.group = g.E * g.H < want ? g.E * g.H : want;
   }
   a.wait_deps = wait_deps;
@@ -969,12 +917,6 @@ cudaError_t launch_fused(const TcPlan* plan, const Geometry& g, int* counters, i
   a.spin_limit = g_spin_limit_override > 0 ? g_spin_limit_override : (1 << 24);
   a.counters = counters;
   a.host_status = host_status_dev;
-#ifdef MA_TRACE
-  a.trace = nullptr;
-  if (const char* t = getenv("MA_B200_TRACE_PTR")) a.trace = reinterpret_cast<long long*>(strtoull(t, nullptr, 16));
-  if (const char* t = getenv("MA_B200_TRACE_STAGE"))
-    if (!(wait_deps == 0 && stage_begin == atoi(t))) a.trace = nullptr;
-#endif
   const int total = (stage_end - stage_begin) * (g.N / kTile) * g.E * g.H;
   const int grid = total < sms ? total : sms;
   void* params[] = {(void*)&plan->maps, (void*)&g, (void*)&a};

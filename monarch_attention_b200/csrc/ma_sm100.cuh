@@ -1,7 +1,7 @@
 // Thin inline-PTX wrappers for the sm_100a features the tensor-core kernels use:
-// mbarriers with bounded waits, TMA tensor loads/stores, tcgen05 (alloc, mma, commit, ld,
-// fences), the shared-memory matrix and instruction descriptors, and 128-byte-swizzle
-// address arithmetic.
+// mbarriers with bounded waits, TMA tensor loads and L2 prefetches, L2 eviction hints and line
+// discards, tcgen05 (mma, commit, ld, st, fences), the shared-memory matrix and instruction
+// descriptors, packed fp32-pair arithmetic, and 128-byte-swizzle address arithmetic.
 #pragma once
 
 #include <cuda.h>
@@ -72,44 +72,14 @@ __device__ __forceinline__ unsigned long long l2_policy_evict_first() {
 __device__ __forceinline__ void l2_discard_line(const void* p) {
   asm volatile("discard.global.L2 [%0], 128;" ::"l"(p) : "memory");
 }
-__device__ __forceinline__ void tma_store_5d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3,
-                                             int c4) {
-  asm volatile("cp.async.bulk.tensor.5d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4, %5}], [%6];" ::"l"(map),
-               "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(src)
-               : "memory");
-}
-__device__ __forceinline__ void tma_store_commit_and_wait() {
-  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-}
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// Shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart.
-// lbo_bytes: distance between 64-element atoms along M/N (only read for MN-major operands).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-  d |= (uint64_t)((1024 >> 4) & 0x3FFF) << 32;
-  d |= (uint64_t)1 << 46;  // descriptor version of this architecture
-  d |= (uint64_t)2 << 61;  // 128-byte swizzle
-  return d;
-}
 // Instruction descriptor for kind::f16 with fp32 accumulation.
 __host__ __device__ constexpr uint32_t instr_desc(int fmt_ab, int a_mn_major, int b_mn_major, int n, int m) {
   return (1u << 4) | ((uint32_t)fmt_ab << 7) | ((uint32_t)fmt_ab << 10) | ((uint32_t)a_mn_major << 15) |
          ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                        uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
 }
 // The same instruction with each descriptor given as its low word; the high word (stride between
 // 8-row groups, descriptor version, swizzle mode) is common to every operand of these kernels.
@@ -272,46 +242,10 @@ __device__ __forceinline__ float2 unpack2<__half>(uint32_t u) {
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
-__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
-}
 
 // Byte offset of 16-byte chunk `chunk` (0..7) of row `row` in a [rows x 128 B] tile with 128-byte swizzle.
 __device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t chunk) { return row * 128u + ((chunk ^ (row & 7u)) << 4); }
 
-// Bounded, abortable wait for roles that are not latency-critical: backs off between attempts so that
-// the waiting warp leaves the issue slots of its scheduler to the warps doing arithmetic.
-__device__ __forceinline__ bool mbar_wait_polite(uint32_t bar, uint32_t parity, const volatile int* abort_flag,
-                                                 unsigned sleep_ns) {
-  for (int it = 0; it < (1 << 21); ++it) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (done) return true;
-    __nanosleep(sleep_ns);
-    if ((it & 255) == 255 && *abort_flag != 0) return false;
-  }
-  return false;
-}
-// Non-blocking test of the phase with the given parity.
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return done != 0;
-}
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -319,15 +253,6 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ bool mbar_wait_abortable(uint32_t bar, uint32_t parity, const volatile int* abort_flag) {
   for (int it = 0; it < (1 << 21); ++it) {
     uint32_t done;
-#ifdef MA_EXP_HINT
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity), "r"(MA_EXP_HINT)
-        : "memory");
-#else
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -335,7 +260,6 @@ __device__ __forceinline__ bool mbar_wait_abortable(uint32_t bar, uint32_t parit
         : "=r"(done)
         : "r"(bar), "r"(parity)
         : "memory");
-#endif
     if (done) return true;
     if ((it & 255) == 255 && *abort_flag != 0) return false;
   }
@@ -352,7 +276,7 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
   asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
 // Named barrier over `threads` threads that also ORs a predicate across them.
 __device__ __forceinline__ bool named_barrier_or(int id, int threads, bool pred) {
   uint32_t out;
@@ -366,13 +290,6 @@ __device__ __forceinline__ bool named_barrier_or(int id, int threads, bool pred)
       : "memory");
   return out != 0;
 }
-__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
-  asm volatile("barrier.cta.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-__device__ __forceinline__ void st_global_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
-
 __device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&w)[8]) {
   asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),
                "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])

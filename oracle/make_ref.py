@@ -1,4 +1,4 @@
-"""Put the reference's own attention package where the benchmark can import it on the GPU box.
+"""Put the reference's own attention package where the benchmark can import it.
 
     python oracle/make_ref.py --ref /path/to/reference
 

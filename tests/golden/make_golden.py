@@ -1,7 +1,7 @@
 """Generate tests/golden/golden.npz from the reference implementation itself.
 
-Run in a container that has the reference checked out (it cannot travel to the
-GPU box, which is why the vectors are committed):
+Run where the reference is checked out (the machines that run the GPU tests do not
+have it, which is why the vectors are committed):
 
     PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py --ref /path/to/reference
 
