@@ -23,25 +23,28 @@
 // normalised in fp32 and then rounded to the storage type before the second contraction, and the
 // column sums cr of the left factor are taken from the factor before that rounding.
 //
-// Inside a CTA (512 threads, one CTA per SM, all 512 tensor-memory columns):
-//   warps 0-3, 4-7   two softmax groups on alternating items, one tile row per thread: the whole row
-//              of S is read from tensor memory into registers once (tcgen05.ld), maximum, exponentials,
-//              row sum and negative entropy are formed there (packed fp32 pairs), the normalised
-//              factor P is rounded to 16 bits and written back over S with tcgen05.st, from where the
-//              second contraction reads it as its A operand.  Only the left-factor stage, which needs
-//              P^T, goes through shared memory: P as a 16-bit value plus a 16-bit remainder, so that
-//              the column sums come out of the tensor core in fp32 precision.
-//   warps 8-11 epilogue group: waits for O, rounds it and stores rows to global memory with 32-byte
+// Inside a CTA (768 threads, one CTA per SM, all 512 tensor-memory columns):
+//   warps 0-15 softmax: four groups of four warps, all on the SAME item.  A tile row is split between
+//              the four threads `row` of the groups (32 columns each; warps w, w+4, w+8, w+12 reach the
+//              same tensor-memory lanes and share a scheduler).  Each thread reads its columns of S into
+//              registers once (tcgen05.ld), takes their maximum, exponentiates against it (packed fp32
+//              pairs), and the four parts of a row exchange (shift, sum, entropy sum) through shared
+//              memory once and rescale.  The normalised factor P is rounded to 16 bits and written to the
+//              item's P buffer in tensor memory (tcgen05.st), from where the second contraction reads it
+//              as its A operand.  Only the left-factor stage, which needs P^T, goes through shared
+//              memory: P as a 16-bit value plus a 16-bit remainder, so that the column sums come out of
+//              the tensor core in fp32 precision.
+//   warps 16-19 epilogue group: waits for O, rounds it and stores rows to global memory with 32-byte
 //              stores and drops the state tiles the item read from L2
-//   warp 12    planner: works out the item schedule, waits for each item's dependency, keeps the
-//              accounts of the operand ring (thirteen 16 KB tiles) and leaves a descriptor per item
-//   warp 15    issuer: issues the item's TMA loads (2-3 operand tiles and the 512-byte row vector cr
+//   warp 20    planner: works out the item schedule, waits for each item's dependency, keeps the
+//              accounts of the operand ring (twelve 16 KB tiles) and leaves a descriptor per item
+//   warp 23    issuer: issues the item's TMA loads (2-3 operand tiles and the 512-byte row vector cr
 //              or cl); each of these instructions blocks for as long as the TMA unit is busy, which is
 //              why nothing else is in this warp
-//   warp 13    MMA issuer 1: S = A B^T for item n (tcgen05.mma, fp32 accumulator S[n%3] in tensor memory);
-//              its second thread is the publisher: device-scope fence and one increment of the
+//   warp 21    MMA issuer 1: S = A B^T for item n (tcgen05.mma, fp32 accumulator in buffer n%3 of tensor
+//              memory); its second thread is the publisher: device-scope fence and one increment of the
 //              item's (head, stage) completion counter
-//   warp 14    MMA issuer 2: the second contraction of item n into O
+//   warp 22    MMA issuer 2: the second contraction of item n, O written over the item's S
 // All hand-offs are mbarriers; every wait is bounded and abortable (see ma_sm100.cuh).
 #include <cuda.h>
 
@@ -61,19 +64,20 @@ constexpr int kTile = 128;
 constexpr int kHead = 64;
 constexpr uint32_t kTileBytes = kTile * kHead * 2;  // 16 KB
 
-constexpr int kEpilogueWarp0 = 8;   // warps 8..11
-constexpr int kPlannerWarp = 12;
-constexpr int kMma1Warp = 13;
-constexpr int kMma2Warp = 14;
-constexpr int kIssuerWarp = 15;
-constexpr int kThreads = 16 * 32;
+constexpr int kGroups = 4;          // softmax warpgroups: threads per tile row
+constexpr int kEpilogueWarp0 = 4 * kGroups;   // four warps
+constexpr int kPlannerWarp = kEpilogueWarp0 + 4;
+constexpr int kMma1Warp = kPlannerWarp + 1;
+constexpr int kMma2Warp = kPlannerWarp + 2;
+constexpr int kIssuerWarp = kPlannerWarp + 3;
+constexpr int kThreads = (kIssuerWarp + 1) * 32;
 
-// Operand tiles live in a ring of thirteen 16 KB tiles.  An item takes two consecutive tiles (A, B) or
+// Operand tiles live in a ring of twelve 16 KB tiles.  An item takes two consecutive tiles (A, B) or
 // three (A, B, V) - never wrapping: if the tail of the ring is too short it is skipped and charged to
-// the item.  Tiles 9..12 double as the P region of the left-factor stage (P and its remainder,
-// 2 x 32 KB): while a left-factor item is in flight the ring ends at tile 9.
-constexpr int kRingTiles = 13;
-constexpr int kRingLeft = 9;
+// the item.  Tiles 8..11 double as the P region of the left-factor stage (P and its remainder,
+// 2 x 32 KB): while a left-factor item is in flight the ring ends at tile 8.
+constexpr int kRingTiles = 12;
+constexpr int kRingLeft = 8;
 constexpr int kSlots = 8;  // items in flight: depth of the per-item barrier / row-vector rings
 // Tensor memory: three 128-column accumulator buffers (columns 0, 128, 256): item n's S = A B^T goes to
 // buffer n % 3, the softmax reads it, and the second contraction writes the item's O over it, so that S
@@ -83,12 +87,12 @@ constexpr int kSlots = 8;  // items in flight: depth of the per-item barrier / r
 constexpr int kSBuffers = 3;
 constexpr uint32_t kTmemP = 384;
 constexpr uint32_t kOffSlots = 0;
-constexpr uint32_t kOffPreg = kRingLeft * kTileBytes;             // P region = ring tiles 9..12
+constexpr uint32_t kOffPreg = kRingLeft * kTileBytes;             // P region = ring tiles 8..11
 constexpr uint32_t kOffOnes = kRingTiles * kTileBytes;            // 16 x 128 K-major operand of ones (4 KB)
 constexpr uint32_t kOffVec = kOffOnes + 4096;                     // kSlots x 512 B (cr or cl of the item)
 constexpr uint32_t kOffStats = kOffVec + kSlots * 512;            // 4 x 128 floats (cl of the item's rows)
-constexpr uint32_t kOffXch = kOffStats + 4 * 128 * 4;              // 2 x 3 x 2 x 128 floats exchanged between the halves of a row
-constexpr uint32_t kOffBar = kOffXch + 2 * 3 * 2 * 128 * 4;
+constexpr uint32_t kOffXch = kOffStats + 4 * 128 * 4;              // 2 x 3 x kGroups x 128 floats exchanged between the parts of a row
+constexpr uint32_t kOffBar = kOffXch + 2 * 3 * kGroups * 128 * 4;
 constexpr int kNumBarsConst = 56;
 constexpr int kDescRing = 16;  // item descriptors; deeper than the planner can run ahead (kSlots)
 constexpr uint32_t kOffDesc = kOffBar + 8 * kNumBarsConst + 16;
@@ -114,7 +118,7 @@ enum {
 };
 static_assert(kNumBars <= kNumBarsConst, "barrier count");
 constexpr int kEpilogueBarrier = 1;  // named barrier of the 128 epilogue threads
-constexpr int kSoftmaxBarrier = 3;   // named barriers 3..6: one per pair of softmax warps that share rows
+constexpr int kSoftmaxBarrier = 3;   // named barriers 3..6: one per set of softmax warps that share rows
 
 struct FusedArgs {
   int stage_begin, stage_end;  // stages [begin, end) of the 2T stages run in this launch
@@ -189,7 +193,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       mbar_init(bar(kBarOFull + i), 1);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(bar(kBarPFull + i), 256);
+      mbar_init(bar(kBarPFull + i), 128 * kGroups);
       mbar_init(bar(kBarPEmpty + i), 1);
     }
     for (int i = 0; i < 4; ++i) {
@@ -246,14 +250,14 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
     }
   };
 
-  // Registers per warpgroup (the launch gives every thread 128): the two softmax groups hold a
-  // whole accumulator row each, the epilogue group half a row, the single-thread roles little.
-  // 256 x 192 + 128 x 80 + 128 x 48 = 65536 = 512 x 128, so the increase can always be granted.
+  // Registers per warpgroup (the launch gives every thread 80): a softmax thread holds 32 accumulator
+  // columns, an epilogue thread half a row of O, the single-thread roles little.
+  // 512 x 72 + 128 x 96 + 128 x 40 = 54272 <= 768 x 80, so the increase can always be granted.
   // (What setmaxnreg redistributes is the allocation the CTA was launched with - threads x registers
   // per thread - not the whole register file: a request beyond that pool blocks for ever.)
 #define ROLE_WAIT(b_, p_) mbar_wait_abortable(b_, p_, abort_flag)
   if (warp >= kPlannerWarp) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
   if (warp == kPlannerWarp) {
     // =========================== planner =================================================
     // The warp works in batches of kBatch items: lane L < kBatch works out item n0 + L of this CTA (the
@@ -499,7 +503,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
     }
   }
   } else if (warp >= kEpilogueWarp0) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 96;");
     // =========================== epilogue group =================================================
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
@@ -598,26 +602,31 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       }
     }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 192;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     // =========================== softmax warps ===========================================
-    // Both groups of four warps work on the SAME item: a row's columns are split between thread `row` of
-    // group 0 and thread `row` of group 1 (warps w and w + 4 reach the same tensor-memory lanes).  All
-    // eight warps then run the same short instruction sequence at the same time - with the groups on
-    // alternating items, every scheduler had two copies of a much longer sequence in flight at different
-    // places and the warps spent more time waiting for instructions than issuing them.  The halves of a
-    // row exchange their maximum and their sums through shared memory (two 256-thread barriers per item).
+    // All kGroups groups of four warps work on the SAME item: a row's columns are split between the
+    // threads `row` of the groups (warps w, w + 4, w + 8, ... reach the same tensor-memory lanes and
+    // share a scheduler).  Every warp then runs the same short instruction sequence at the same time,
+    // and a scheduler has kGroups of them to hide one another's latencies - with two groups of one
+    // thread per row on alternating items, every scheduler had two copies of a four times longer
+    // sequence in flight at different places, and the warps spent more time waiting for instructions
+    // than issuing them.  Each part of a row is exponentiated against its OWN maximum; the parts then
+    // exchange (shift, sum, entropy sum) through shared memory once and rescale.
     const int grp = warp >> 2;
     const int row = (warp & 3) * 32 + lane;         // tensor-memory lane = tile row
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     // With two blocks per tile only the 64-column half that belongs to the row's own block or column
     // means anything (rows are blk*64 + j in the right-factor tiles and jj*64 + l in the column tiles;
     // columns are blk*64 + i, or jj*64 + m); the other half of P is zero.
-    const int h0 = per > 1 ? (row >> 6) : 0;  // uniform within a warp
-    constexpr int kMine = 64 / PER;           // columns of the row this thread works on
-    const int col0 = per > 1 ? 64 * h0 + 32 * grp : 64 * grp;  // first of them
-    float* xch_base = reinterpret_cast<float*>(base_ptr + kOffXch);  // [2][3][2][128]: shift, sum, entropy sum per half row
+    const int h0 = per > 1 ? (row >> 6) : 0;    // uniform within a warp
+    constexpr int kOwn = 128 / PER;             // columns of the row that mean anything
+    constexpr int kMine = kOwn / kGroups;       // columns this thread works on
+    static_assert(kMine == 32 || kMine == 16, "tensor-memory access shapes below");
+    const int col0 = (per > 1 ? 64 * h0 : 0) + kMine * grp;  // first of them
+    float* xch_base = reinterpret_cast<float*>(base_ptr + kOffXch);  // [2][3][kGroups][128]: shift, sum, entropy sum per part
     for (int n = 0; n < n_items; ++n) {
-      float* xch = xch_base + (n & 1) * 768;  // by item parity: a fast thread's next item must not overwrite what a slow one still reads
+      // by item parity: a fast thread's next item must not overwrite what a slow one still reads
+      float* xch = xch_base + (n & 1) * (3 * kGroups * 128);
       const int slot = n % kSlots, sb = n % kSBuffers, pb = n & 1;
       const float* vec = reinterpret_cast<const float*>(base_ptr + kOffVec + slot * 512);
       bool ok = mbar_wait_abortable(bar(kBarInFull + slot), (uint32_t)(n / kSlots) & 1u, abort_flag);
@@ -632,19 +641,21 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       // This thread's columns of S, read once and kept in registers.
       float s[kMine];
       if (ok) {
-#pragma unroll
-        for (int c = 0; c < kMine / 32; ++c)
-          tmem_ld32_nowait(tmem_s + col0 + 32 * c, *reinterpret_cast<float(*)[32]>(&s[32 * c]));
-#pragma unroll
-        for (int c = 0; c < kMine / 32; ++c) tmem_wait_ld(*reinterpret_cast<float(*)[32]>(&s[32 * c]));
+        if (kMine == 32) {
+          tmem_ld32_nowait(tmem_s + col0, *reinterpret_cast<float(*)[32]>(&s[0]));
+          tmem_wait_ld(*reinterpret_cast<float(*)[32]>(&s[0]));
+        } else {
+          tmem_ld16_nowait(tmem_s + col0, *reinterpret_cast<float(*)[16]>(&s[0]));
+          tmem_wait_ld16(*reinterpret_cast<float(*)[16]>(&s[0]));
+        }
       } else {
 #pragma unroll
         for (int i = 0; i < kMine; ++i) s[i] = 0.f;
       }
 
-      // Pass 1: maximum of this half row.  Right-factor stages: of S itself (rounding is monotonic, so the
-      // maximum of the rounded logits is the rounded maximum).  Left-factor / output stages: the logits
-      // round(S) - cl[m] are formed in place first.
+      // Pass 1: maximum of this part of the row.  Right-factor stages: of S itself (rounding is
+      // monotonic, so the maximum of the rounded logits is the rounded maximum).  Left-factor / output
+      // stages: the logits round(S) - cl[m] are formed in place first.
       float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
       if (right) {
 #pragma unroll
@@ -672,12 +683,11 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           s[i + 4] = c.x; s[i + 5] = c.y; s[i + 6] = d.x; s[i + 7] = d.y;
         }
       }
-      // Each half row is exponentiated against its OWN maximum; the halves then exchange (shift, sum,
-      // entropy sum) once and rescale - one barrier per item instead of two.  With top the shift of the
-      // whole row (the larger of the two: max(max(a, eps), max(b, eps)) = max(max(a, b), eps)) and
-      // c = 2^(shift_h - top) <= 1:   e_i = c e'_i,   sum e_i log2 e_i = c (sum e'_i u'_i + log2(c) sum e'_i).
+      // With top the shift of the whole row (the largest of the parts': max(max(a, eps), max(b, eps)) =
+      // max(max(a, b), eps)) and c = 2^(shift_part - top) <= 1:
+      //   e_i = c e'_i,   sum e_i log2 e_i = c (sum e'_i u'_i + log2(c) sum e'_i).
       const float hmax = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-      float my_off, part_sum, part_ent = 0.f;  // my_off: this half's shift in log2 units
+      float my_off, part_sum, part_ent = 0.f;  // my_off: this part's shift in log2 units
       if (right) {
         // x = sm_scale * round(S) / (cr + eps), clamp on the maximum from below
         const float row_scale = g.sm_scale / ((it.first ? 1.0f : vec[row]) + kEps);
@@ -716,49 +726,49 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         part_sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
       }
       xch[grp * 128 + row] = my_off;
-      xch[256 + grp * 128 + row] = part_sum;
-      xch[512 + grp * 128 + row] = part_ent;
-      // the exchange, between the two warps that share the rows (they also share a scheduler, so they get
-      // here together); also the one place where the pair agrees to leave (a thread that went on or left
-      // alone would strand its partners at the barrier)
-      if (named_barrier_or(kSoftmaxBarrier + (warp & 3), 64, !ok)) {
+      xch[(kGroups + grp) * 128 + row] = part_sum;
+      xch[(2 * kGroups + grp) * 128 + row] = part_ent;
+      // the exchange, between the warps that share the rows (they also share a scheduler, so they get here
+      // together); also the one place where they agree to leave (a thread that went on or left alone
+      // would strand its partners at the barrier)
+      if (named_barrier_or(kSoftmaxBarrier + (warp & 3), 32 * kGroups, !ok)) {
         if (!ok) give_up(401);
         break;
       }
-      // (both halves evaluate the same expressions on the same six numbers, so they get the same bits)
-      const float off0 = xch[row], off1 = xch[128 + row];
-      const float top = fmaxf(off0, off1);
-      const float c0 = ex2(off0 - top), c1 = ex2(off1 - top);
-      const float s0 = xch[256 + row], s1 = xch[384 + row];
-      const float row_sum = c0 * s0 + c1 * s1;
+      // (all parts evaluate the same expressions on the same numbers, so they get the same bits)
+      float offs[kGroups], sums[kGroups];
+      float top = -INFINITY;
+#pragma unroll
+      for (int q = 0; q < kGroups; ++q) {
+        offs[q] = xch[q * 128 + row];
+        sums[q] = xch[(kGroups + q) * 128 + row];
+        top = fmaxf(top, offs[q]);
+      }
+      float row_sum = 0.f, my_c = 1.f;
+#pragma unroll
+      for (int q = 0; q < kGroups; ++q) {
+        offs[q] -= top;                 // log2 of the part's factor c
+        const float c = ex2(offs[q]);
+        if (q == grp) my_c = c;
+        sums[q] *= c;
+        row_sum += sums[q];
+      }
       // 1 / sum by the approximate reciprocal (1 ulp; the quotient is rounded to 16 bits right after) - the
       // exact one is a long dependent sequence on the path of every item
       const float denom = right ? row_sum + kEps : row_sum;
       float rden;
       asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rden) : "f"(denom));
-      // this half's exponentials were taken against its own shift.  al = sm_scale * (P k): the scale is a
+      // this part's exponentials were taken against its own shift.  al = sm_scale * (P k): the scale is a
       // power of two (D = 64), so it can ride on P exactly; the stage with V keeps P unscaled (y = P v)
       // and scales the al half in the epilogue
-      float inv = rden * (grp == 0 ? c0 : c1);
+      float inv = rden * my_c;
       if (it.kind == kStageRight) inv *= g.sm_scale;
-      // cl of the row for the epilogue group, off the path to P: sum_i r_i ln r_i with r_i = e_i / denom and
-      // ln e_i = ln2 * u_i.  The 4-deep ring cannot be overrun: the first contraction of item n+4 needs the
-      // accumulator buffer of item n+1 back from the epilogue, which takes the items in order.
-      auto post_stat = [&]() {
-        if (grp == 0) {
-          if (right) {
-            const float row_ent = c0 * (xch[512 + row] + (off0 - top) * s0) + c1 * (xch[640 + row] + (off1 - top) * s1);
-            reinterpret_cast<float*>(base_ptr + kOffStats)[(n & 3) * 128 + row] = (kLn2 * row_ent - __logf(denom) * row_sum) * rden;
-          }
-          mbar_arrive(bar(kBarStat + (n & 3)));
-        }
-      };
 
       const float2 invv = make_float2(inv, inv);
       if (it.kind != kStageLeft) {
         // Pass 3: P = round(e / sum) into the item's P buffer in tensor memory: A operand of the second
         // contraction.  (The buffer is free once the second contraction of item n - 2 has completed - long
-        // ago, as a rule.  A wait that runs out is reported and noticed at the next item's first barrier.)
+        // ago, as a rule.  A wait that runs out is reported and noticed at the next item's barrier.)
         if (!mbar_wait_abortable(bar(kBarPEmpty + pb), ((uint32_t)(n >> 1) & 1u) ^ 1u, abort_flag)) give_up(404);
         tc_fence_after();
         const uint32_t tmem_p = tmem + lane_base + kTmemP + pb * 64;
@@ -768,28 +778,32 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
           const float2 r = mul2(make_float2(s[2 * i], s[2 * i + 1]), invv);
           pk[i] = pack2<T>(r.x, r.y);
         }
-        if (per == 1) {
-          tmem_st32(tmem_p + 32 * grp, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
+        // cells (two columns each) of this thread's columns; with two blocks per tile, zeros in the
+        // matching cells of the other half
+        const uint32_t cell0 = (uint32_t)(col0 >> 1);
+        if (kMine == 32) {
+          tmem_st16(tmem_p + cell0, *reinterpret_cast<uint32_t(*)[16]>(&pk[0]));
         } else {
-          tmem_st16(tmem_p + 32 * h0 + 16 * grp, *reinterpret_cast<uint32_t(*)[16]>(&pk[0]));
+          tmem_st8(tmem_p + cell0, *reinterpret_cast<uint32_t(*)[8]>(&pk[0]));
+          if (per > 1) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) pk[i] = 0u;
-          tmem_st16(tmem_p + 32 * (1 - h0) + 16 * grp, *reinterpret_cast<uint32_t(*)[16]>(&pk[0]));
+            for (int i = 0; i < 8; ++i) pk[i] = 0u;
+            tmem_st8(tmem_p + (cell0 ^ 32u), *reinterpret_cast<uint32_t(*)[8]>(&pk[0]));
+          }
         }
         tmem_wait_st();
         tc_fence_before();
       } else {
-        // P^T goes through shared memory (MN-major A operand): rounded P in tiles 9, 10 of the ring, the
-        // rounded remainder P - round(P) in tiles 11, 12.  Wait until the item that used the region last
-        // has completed its second contraction.
+        // P^T goes through shared memory (MN-major A operand): rounded P in the first two tiles of the P
+        // region, the rounded remainder P - round(P) in the other two.  Wait until the item that used the
+        // region last has completed its second contraction.
         if (it.p_dist > 0) {
           const int m = n - it.p_dist;
           if (!mbar_wait_abortable(bar(kBarInEmpty + m % kSlots), (uint32_t)(m / kSlots) & 1u, abort_flag)) give_up(403);
         }
         const uint32_t sP = base + kOffPreg;
-        // 16-byte groups of this thread's columns: atom (64 columns) and group within it
-        const uint32_t atom = per > 1 ? (uint32_t)h0 : (uint32_t)grp;
-        const uint32_t g0 = per > 1 ? 4u * (uint32_t)grp : 0u;
+        // 16-byte groups (8 columns) of this thread's columns: 64-column atom and group within it
+        const uint32_t atom = (uint32_t)col0 >> 6, g0 = ((uint32_t)col0 & 63u) >> 3;
 #pragma unroll
         for (int c8 = 0; c8 < kMine / 8; ++c8) {
           uint32_t hi[4], lo[4];
@@ -806,8 +820,8 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         }
         if (per > 1) {
 #pragma unroll
-          for (int c8 = 0; c8 < 4; ++c8) {
-            const uint32_t off = (uint32_t)(1 - h0) * kTileBytes + swz(row, g0 + c8);
+          for (int c8 = 0; c8 < kMine / 8; ++c8) {
+            const uint32_t off = (atom ^ 1u) * kTileBytes + swz(row, g0 + c8);
             st_shared_v4(sP + off, 0u, 0u, 0u, 0u);
             st_shared_v4(sP + 2 * kTileBytes + off, 0u, 0u, 0u, 0u);
           }
@@ -815,7 +829,22 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         fence_async_smem();
       }
       mbar_arrive(bar(kBarPFull + pb));
-      post_stat();
+      // cl of the row for the epilogue group, off the path to P: sum_i r_i ln r_i with r_i = e_i / denom and
+      // ln e_i = ln2 * u_i.  The 4-deep ring cannot be overrun: the first contraction of item n+4 needs the
+      // accumulator buffer of item n+1 back from the epilogue, which takes the items in order.
+      if (grp == 0) {
+        if (right) {
+          float row_ent = 0.f;
+#pragma unroll
+          for (int q = 0; q < kGroups; ++q) {
+            // sums[q] = c s', offs[q] = log2 c:  c (E' + log2(c) s') = c E' + log2(c) (c s')
+            const float c = ex2(offs[q]);
+            row_ent += c * xch[(2 * kGroups + q) * 128 + row] + offs[q] * sums[q];
+          }
+          reinterpret_cast<float*>(base_ptr + kOffStats)[(n & 3) * 128 + row] = (kLn2 * row_ent - __logf(denom) * row_sum) * rden;
+        }
+        mbar_arrive(bar(kBarStat + (n & 3)));
+      }
     }
   }
 
