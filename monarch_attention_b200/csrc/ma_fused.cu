@@ -71,6 +71,11 @@ constexpr int kMma1Warp = kPlannerWarp + 1;
 constexpr int kMma2Warp = kPlannerWarp + 2;
 constexpr int kIssuerWarp = kPlannerWarp + 3;
 constexpr int kThreads = (kIssuerWarp + 1) * 32;
+// Registers per thread after setmaxnreg, by role.  What setmaxnreg redistributes is the allocation the CTA
+// was launched with (threads x registers per thread at launch), not the whole register file: a request
+// beyond that pool blocks for ever, so the host checks the sum against the compiled kernel before it launches.
+constexpr int kRegsSoftmax = 72, kRegsEpilogue = 96, kRegsSingle = 40;
+constexpr int kRegPool = 4 * kGroups * 32 * kRegsSoftmax + 128 * kRegsEpilogue + 128 * kRegsSingle;
 
 // Operand tiles live in a ring of twelve 16 KB tiles.  An item takes two consecutive tiles (A, B) or
 // three (A, B, V) - never wrapping: if the tail of the ring is too short it is skipped and charged to
@@ -250,14 +255,12 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
     }
   };
 
-  // Registers per warpgroup (the launch gives every thread 80): a softmax thread holds 32 accumulator
-  // columns, an epilogue thread half a row of O, the single-thread roles little.
-  // 512 x 72 + 128 x 96 + 128 x 40 = 54272 <= 768 x 80, so the increase can always be granted.
-  // (What setmaxnreg redistributes is the allocation the CTA was launched with - threads x registers
-  // per thread - not the whole register file: a request beyond that pool blocks for ever.)
+  // Registers per role (kRegsSoftmax / kRegsEpilogue / kRegsSingle; the launch gives every thread 80): a
+  // softmax thread holds 32 accumulator columns, an epilogue thread a 64-column row of O, the single-thread
+  // roles little.
 #define ROLE_WAIT(b_, p_) mbar_wait_abortable(b_, p_, abort_flag)
   if (warp >= kPlannerWarp) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsSingle));
   if (warp == kPlannerWarp) {
     // =========================== planner =================================================
     // The warp works in batches of kBatch items: lane L < kBatch works out item n0 + L of this CTA (the
@@ -503,7 +506,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
     }
   }
   } else if (warp >= kEpilogueWarp0) {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 96;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsEpilogue));
     // =========================== epilogue group =================================================
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
@@ -602,7 +605,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       }
     }
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
     // =========================== softmax warps ===========================================
     // All kGroups groups of four warps work on the SAME item: a row's columns are split between the
     // threads `row` of the groups (warps w, w + 4, w + 8, ... reach the same tensor-memory lanes and
@@ -906,6 +909,13 @@ cudaError_t launch_fused(const TcPlan* plan, const Geometry& g, int* counters, i
       if (e != cudaSuccess) return e;
       e = cudaDeviceGetAttribute(&g_sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
       if (e != cudaSuccess) return e;
+      cudaFuncAttributes fa;
+      e = cudaFuncGetAttributes(&fa, fn);
+      if (e != cudaSuccess) return e;
+      // a build whose launch allocation cannot cover the roles' requests must not start: setmaxnreg would block
+      // (and the decreases must really be decreases, the increase an increase)
+      if (fa.numRegs * kThreads < kRegPool || fa.numRegs < kRegsSoftmax || fa.numRegs < kRegsSingle || fa.numRegs > kRegsEpilogue)
+        return cudaErrorLaunchOutOfResources;
       g_attr_done[dev][variant] = true;
     }
     HostStatus& hs = g_host_status[dev];

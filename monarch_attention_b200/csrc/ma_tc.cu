@@ -82,6 +82,7 @@ bool tc_supported(const Geometry& g, int qk_dtype, int v_dtype, const char** why
   if (g.N != g.B * g.M) return no("needs N = block size * block count (no padding)");
   if (g.mask != nullptr) return no("mask not handled on this path");
   if ((long long)g.E * g.H > 65535) return no("E*H too large for the grid");
+  if (g.T > 2047) return no("more than 2047 iterations (the stage index of an item descriptor has twelve bits)");
   if (g.q.ptr != nullptr) {  // layout queries pass no pointers
     if (!view_ok(g.q, g.E, g.H) || !view_ok(g.k, g.E, g.H) || !view_ok(g.v, g.E, g.H) || !view_ok(g.out, g.E, g.H))
       return no("q, k, v, out need 16-byte aligned bases and strides that are non-zero multiples of 8 elements");
