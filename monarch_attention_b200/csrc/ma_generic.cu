@@ -39,6 +39,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 template <typename T>
 __device__ __forceinline__ float dot_row(const float* __restrict__ a, const T* __restrict__ row, int D) {
   float acc = 0.f;
+#pragma unroll 8
   for (int d = 0; d < D; ++d) acc = fmaf(a[d], Cvt<T>::to_f(row[d]), acc);
   return acc;
 }
@@ -46,6 +47,7 @@ __device__ __forceinline__ float dot_row(const float* __restrict__ a, const T* _
 // The same dot product with the row already converted to fp32 in shared memory.
 __device__ __forceinline__ float dot_smem(const float* __restrict__ a, const float* __restrict__ row, int D) {
   float acc = 0.f;
+#pragma unroll 8
   for (int d = 0; d < D; ++d) acc = fmaf(a[d], row[d], acc);
   return acc;
 }
@@ -169,6 +171,7 @@ __global__ void __launch_bounds__(kThreads) right_stage_kernel(const Geometry g,
     for (int d = lane; d < D; d += 32) {
       float acc = 0.f;
       if (sK) {
+#pragma unroll 8
         for (int i = 0; i < B; ++i) acc = fmaf(round_through<TQ>(rbuf[i]), sK[(size_t)i * (D + 1) + d], acc);
       } else {
         for (int i = 0; i < B; ++i) {
@@ -183,6 +186,7 @@ __global__ void __launch_bounds__(kThreads) right_stage_kernel(const Geometry g,
       for (int d = lane; d < Dv; d += 32) {
         float acc = 0.f;
         if (sV) {
+#pragma unroll 8
           for (int i = 0; i < B; ++i) acc = fmaf(round_through<TV>(rbuf[i]), sV[(size_t)i * (Dv + 1) + d], acc);
         } else {
           for (int i = 0; i < B; ++i) {
@@ -266,10 +270,12 @@ __global__ void __launch_bounds__(kThreads) left_stage_kernel(const Geometry g, 
       // same products in the same order as pass 1 (fmaf(a, b, acc) with a, b swapped is identical)
       if (sQ) {
         const float* qs = sQ + (size_t)l * (D + 1);
+#pragma unroll 8
         for (int d = 0; d < D; ++d) dot = fmaf(qs[d], avec[d], dot);
       } else {
         const TQ* qrow = token_row<TQ>(g.q, e, h, l * B + j, g.pad_off, g.N);
         if (qrow)
+#pragma unroll 8
           for (int d = 0; d < D; ++d) dot = fmaf(Cvt<TQ>::to_f(qrow[d]), avec[d], dot);
       }
       float w = round_through<TQ>(dot) - c;
@@ -283,6 +289,7 @@ __global__ void __launch_bounds__(kThreads) left_stage_kernel(const Geometry g, 
     for (int d = lane; d < D; d += 32) {
       float acc = 0.f;
       if (sQ) {
+#pragma unroll 8
         for (int l = 0; l < M; ++l) acc = fmaf(round_through<TQ>(rbuf[l]), sQ[(size_t)l * (D + 1) + d], acc);
       } else {
         for (int l = 0; l < M; ++l) {
@@ -345,16 +352,19 @@ __global__ void __launch_bounds__(kThreads) output_stage_kernel(const Geometry g
       vsum += ex;
     }
     vsum = warp_sum(vsum);
+    // the factor is normalised and rounded to the value type once per row (:59-61)
+    for (int mm = lane; mm < M; mm += 32) rbuf[mm] = round_through<TV>(rbuf[mm] / vsum);
     __syncwarp();
     TV* orow = reinterpret_cast<TV*>(const_cast<void*>(g.out.ptr)) + (long long)e * g.out.se +
                (long long)h * g.out.sh + (long long)n * g.out.sn;
     for (int d = lane; d < Dv; d += 32) {
       float acc = 0.f;
       if (sY) {
-        for (int mm = 0; mm < M; ++mm) acc = fmaf(round_through<TV>(rbuf[mm] / vsum), sY[(size_t)mm * (Dv + 1) + d], acc);
+#pragma unroll 8
+        for (int mm = 0; mm < M; ++mm) acc = fmaf(rbuf[mm], sY[(size_t)mm * (Dv + 1) + d], acc);
       } else {
-        for (int mm = 0; mm < M; ++mm)
-          acc = fmaf(round_through<TV>(rbuf[mm] / vsum), Cvt<TV>::to_f(y[(long long)mm * Dv + d]), acc);
+#pragma unroll 4
+        for (int mm = 0; mm < M; ++mm) acc = fmaf(rbuf[mm], Cvt<TV>::to_f(y[(long long)mm * Dv + d]), acc);
       }
       orow[d] = Cvt<TV>::from_f(acc);
     }
