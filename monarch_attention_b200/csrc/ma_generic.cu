@@ -372,6 +372,178 @@ __global__ void __launch_bounds__(kThreads) output_stage_kernel(const Geometry g
   }
 }
 
+// ---------------------------------------------------------------------------------
+// Small tiles: block size and block count up to 16 (the reference's own CPU-sized configuration,
+// 16 x 16 blocks of fp32).  Same arithmetic, same rounding points and the same order of every sum as the
+// kernels above - the results are bit-identical - but one THREAD per logit instead of one warp per row:
+// thread t of the 256 owns (row t / 16, key t % 16) of the 16 x 16 tile, a row's softmax is a reduction
+// over a half-warp, and the weighted sums are taken by the same thread grid as (row, 16 features at a
+// time).  A row-per-warp kernel leaves half of its lanes idle on such tiles and spends most of its
+// instructions on loop and address arithmetic.
+// ---------------------------------------------------------------------------------
+constexpr int kSmallMax = 16;
+
+__device__ __forceinline__ float half_max(float v) {  // over the 16 lanes that share a row
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float half_sum(float v) {
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+// rows r = 0..15 (zero beyond `rows`) of a user tensor at padded positions p0 + r * pstep, pitch W + 1
+template <typename T>
+__device__ __forceinline__ void small_token_rows(float* dst, const View4& t, int e, int h, int p0, int pstep, int rows,
+                                                 int W, const Geometry& g) {
+  const int r = threadIdx.x >> 4, c = threadIdx.x & 15;
+  const T* row = r < rows ? token_row<T>(t, e, h, p0 + r * pstep, g.pad_off, g.N) : nullptr;
+  for (int d = c; d < W; d += 16) dst[r * (W + 1) + d] = row ? Cvt<T>::to_f(row[d]) : 0.f;
+}
+template <typename T>
+__device__ __forceinline__ void small_dense_rows(float* dst, const T* src, int rows, int W) {
+  const int r = threadIdx.x >> 4, c = threadIdx.x & 15;
+  for (int d = c; d < W; d += 16) dst[r * (W + 1) + d] = r < rows ? Cvt<T>::to_f(src[(long long)r * W + d]) : 0.f;
+}
+// sum_i w[i] * rows[i][d] in increasing i, for this thread's row weights and the features d = c, c + 16, ...
+template <typename TR, typename F>
+__device__ __forceinline__ void small_weighted_sums(const float* w, const float* rows, int n, int W, int c, F&& emit) {
+  for (int d = c; d < W; d += 16) {
+    float acc = 0.f;
+#pragma unroll 8
+    for (int i = 0; i < n; ++i) acc = fmaf(round_through<TR>(w[i]), rows[i * (W + 1) + d], acc);
+    emit(d, acc);
+  }
+}
+
+template <typename TQ, typename TV, bool WITH_V>
+__global__ void __launch_bounds__(256) small_right_kernel(const Geometry g, const int first) {
+  extern __shared__ float smem[];
+  const int m = blockIdx.y, eh = blockIdx.x, e = eh / g.H, h = eh % g.H;
+  const int B = g.B, D = g.D, Dv = g.Dv, M = g.M;
+  const int j = threadIdx.x >> 4, i = threadIdx.x & 15;
+  float* sA = smem;                       // ar (or q) rows of the block
+  float* sK = sA + kSmallMax * (D + 1);
+  float* sV = sK + kSmallMax * (D + 1);
+  float* sR = sV + (WITH_V ? kSmallMax * (Dv + 1) : 0);  // [16][17] factor rows
+  if (first) small_token_rows<TQ>(sA, g.q, e, h, m * B, 1, B, D, g);
+  else small_dense_rows<TQ>(sA, reinterpret_cast<const TQ*>(g.ar) + ((long long)eh * M + m) * B * D, B, D);
+  small_token_rows<TQ>(sK, g.k, e, h, m * B, 1, B, D, g);
+  if (WITH_V) small_token_rows<TV>(sV, g.v, e, h, m * B, 1, B, Dv, g);
+  __syncthreads();
+
+  const bool live = j < B && i < B;
+  float x = -INFINITY;
+  if (live) {
+    const float crj = first ? 1.0f : g.cr[((long long)eh * M + m) * B + j];
+    const float dot = dot_smem(sA + j * (D + 1), sK + i * (D + 1), D);
+    x = (g.sm_scale * round_through<TQ>(dot)) / (crj + kEps);
+    if (!token_valid(g, e, m * B + i)) x = -INFINITY;
+  }
+  const float vmax = fmaxf(half_max(x), kEps);
+  const float ex = live ? expf(x - vmax) : 0.f;
+  const float vsum = half_sum(ex) + kEps;
+  const float r = fmaxf(ex / vsum, kTiny);
+  const float ent = half_sum(live ? r * logf(r) : 0.f);
+  if (live && i == 0) g.cl[((long long)eh * B + j) * M + m] = ent;
+  sR[j * 17 + i] = live ? r : 0.f;
+  __syncthreads();
+  if (j < B) {
+    TQ* al = reinterpret_cast<TQ*>(g.al) + (((long long)eh * B + j) * M + m) * D;
+    // sm_scale * (r @ k): the product is rounded to storage, scaled, rounded again (:21)
+    small_weighted_sums<TQ>(sR + j * 17, sK, B, D, i,
+                            [&](int d, float acc) { al[d] = Cvt<TQ>::from_f(g.sm_scale * round_through<TQ>(acc)); });
+    if (WITH_V) {
+      TV* y = reinterpret_cast<TV*>(g.y) + (((long long)eh * B + j) * M + m) * Dv;
+      small_weighted_sums<TV>(sR + j * 17, sV, B, Dv, i, [&](int d, float acc) { y[d] = Cvt<TV>::from_f(acc); });
+    }
+  }
+}
+
+template <typename TQ>
+__global__ void __launch_bounds__(256) small_left_kernel(const Geometry g) {
+  extern __shared__ float smem[];
+  const int j = blockIdx.y, eh = blockIdx.x, e = eh / g.H, h = eh % g.H;
+  const int B = g.B, D = g.D, M = g.M;
+  const int l = threadIdx.x >> 4, mm = threadIdx.x & 15;
+  float* sQ = smem;                        // query column j: rows l
+  float* sAL = sQ + kSmallMax * (D + 1);   // al[j]: rows m
+  float* sP = sAL + kSmallMax * (D + 1);   // [m][17]: factor, transposed for the sums over l
+  small_token_rows<TQ>(sQ, g.q, e, h, j, B, M, D, g);
+  small_dense_rows<TQ>(sAL, reinterpret_cast<const TQ*>(g.al) + ((long long)eh * B + j) * M * D, M, D);
+  __syncthreads();
+  const bool live = l < M && mm < M;
+  float w = -INFINITY;
+  if (live) {
+    const float dot = dot_smem(sQ + l * (D + 1), sAL + mm * (D + 1), D);
+    w = round_through<TQ>(dot) - g.cl[((long long)eh * B + j) * M + mm];
+  }
+  const float vmax = half_max(w);
+  const float vsum = half_sum(live ? expf(w - vmax) : 0.f);
+  float p = 0.f;
+  if (live) p = (token_valid(g, e, l * B + j) ? 1.f : 0.f) * (expf(w - vmax) / vsum);
+  sP[mm * 17 + l] = p;
+  __syncthreads();
+  if (l < M) {  // this thread group now works on block row m = l
+    const int m = l, c = mm;
+    const float* prow = sP + m * 17;
+    if (c == 0) {
+      // the sum over l in the order of a butterfly reduction over 32 lanes of which the upper 16 hold zeros
+      float t[16];
+#pragma unroll
+      for (int q = 0; q < 16; ++q) t[q] = q < M ? prow[q] : 0.f;
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1)
+#pragma unroll
+        for (int q = 0; q < o; ++q) t[q] = t[q] + t[q + o];
+      g.cr[((long long)eh * M + m) * B + j] = t[0];
+    }
+    TQ* ar = reinterpret_cast<TQ*>(g.ar) + (((long long)eh * M + m) * B + j) * D;
+    small_weighted_sums<TQ>(prow, sQ, M, D, c, [&](int d, float acc) { ar[d] = Cvt<TQ>::from_f(acc); });
+  }
+}
+
+template <typename TQ, typename TV>
+__global__ void __launch_bounds__(256) small_output_kernel(const Geometry g) {
+  extern __shared__ float smem[];
+  const int j = blockIdx.y, eh = blockIdx.x, e = eh / g.H, h = eh % g.H;
+  const int B = g.B, D = g.D, Dv = g.Dv, M = g.M;
+  const int l = threadIdx.x >> 4, mm = threadIdx.x & 15;
+  float* sQ = smem;
+  float* sAL = sQ + kSmallMax * (D + 1);
+  float* sY = sAL + kSmallMax * (D + 1);
+  float* sP = sY + kSmallMax * (Dv + 1);  // [l][17]
+  small_token_rows<TQ>(sQ, g.q, e, h, j, B, M, D, g);
+  small_dense_rows<TQ>(sAL, reinterpret_cast<const TQ*>(g.al) + ((long long)eh * B + j) * M * D, M, D);
+  small_dense_rows<TV>(sY, reinterpret_cast<const TV*>(g.y) + ((long long)eh * B + j) * M * Dv, M, Dv);
+  __syncthreads();
+  const bool live = l < M && mm < M;
+  float w = -INFINITY;
+  if (live) {
+    const float dot = dot_smem(sQ + l * (D + 1), sAL + mm * (D + 1), D);
+    w = round_through<TQ>(dot) - g.cl[((long long)eh * B + j) * M + mm];
+  }
+  const float vmax = half_max(w);
+  const float ex = live ? expf(w - vmax) : 0.f;
+  const float vsum = half_sum(ex);
+  sP[l * 17 + mm] = live ? round_through<TV>(ex / vsum) : 0.f;
+  __syncthreads();
+  const int n = l * B + j - g.pad_off;
+  if (l < M && n >= 0 && n < g.N) {  // padding rows are dropped from the output (:108)
+    TV* orow = reinterpret_cast<TV*>(const_cast<void*>(g.out.ptr)) + (long long)e * g.out.se + (long long)h * g.out.sh +
+               (long long)n * g.out.sn;
+    small_weighted_sums<float>(sP + l * 17, sY, M, Dv, mm, [&](int d, float acc) { orow[d] = Cvt<TV>::from_f(acc); });
+  }
+}
+
+size_t small_smem_bytes(const Geometry& g) {
+  return ((size_t)kSmallMax * (2 * (g.D + 1) + (g.Dv + 1)) + kSmallMax * 17) * sizeof(float);
+}
+bool small_tiles(const Geometry& g) {
+  return g.B <= kSmallMax && g.M <= kSmallMax && small_smem_bytes(g) <= 48 * 1024;
+}
+
 // Which operand tiles go to shared memory (kStage* bits) and the bytes that takes on top of `base`.
 // Tiles are added while the total stays within 160 KB; a tile that does not fit is read from global
 // memory as before (the explicit-matrix case, whose value rows are N wide, is the usual one).
@@ -404,6 +576,16 @@ cudaError_t launch_typed(const Geometry& g, StageKind kind, bool first, cudaStre
     return cudaSuccess;
   };
   cudaError_t err = cudaSuccess;
+  if (small_tiles(g)) {
+    const size_t sm = small_smem_bytes(g);
+    switch (kind) {
+      case kStageRight: small_right_kernel<TQ, TV, false><<<dim3(EH, g.M), 256, sm, stream>>>(g, first ? 1 : 0); break;
+      case kStageRightWithV: small_right_kernel<TQ, TV, true><<<dim3(EH, g.M), 256, sm, stream>>>(g, first ? 1 : 0); break;
+      case kStageLeft: small_left_kernel<TQ><<<dim3(EH, g.B), 256, sm, stream>>>(g); break;
+      case kStageOutput: small_output_kernel<TQ, TV><<<dim3(EH, g.B), 256, sm, stream>>>(g); break;
+    }
+    return cudaGetLastError();
+  }
   switch (kind) {
     case kStageRight:
       if ((err = raise((const void*)right_stage_kernel<TQ, TV, false>)) != cudaSuccess) return err;
