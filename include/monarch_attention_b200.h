@@ -154,6 +154,12 @@ MA_B200_API int ma_b200_poll_device_status(int device);
 MA_B200_API int ma_b200_selftest_wait_expiry(const ma_b200_problem* p, void* workspace, size_t workspace_bytes,
                                              void* stream);
 
+/* Test hook (no counterpart in the reference): with on != 0 the generic kernel family always runs its
+ * general warp-per-row form, also on tiles of up to 16 x 16 where it would take the thread-per-logit
+ * form.  The two forms are meant to return the same bits; tests/test_parity_gpu.py holds them to that.
+ * Process-wide; 0 restores the default. */
+MA_B200_API void ma_b200_selftest_generic_general_form(int on);
+
 /* Human-readable text for a return code. */
 MA_B200_API const char* ma_b200_status_string(int status);
 

@@ -23,7 +23,7 @@ EXPORTS = (
     "ma_b200_device_status", "ma_b200_status_string", "ma_b200_last_error", "ma_b200_abi_version",
     "ma_b200_forward_static_scratch", "ma_b200_static_scratch_bytes", "ma_b200_static_scratch_last_error",
     "ma_b200_host_scratch_bytes", "ma_b200_forward_host", "ma_b200_host_last_error",
-    "ma_b200_poll_device_status", "ma_b200_selftest_wait_expiry",
+    "ma_b200_poll_device_status", "ma_b200_selftest_wait_expiry", "ma_b200_selftest_generic_general_form",
 )
 
 
@@ -75,6 +75,8 @@ def load() -> C.CDLL:
     lib.ma_b200_poll_device_status.restype = C.c_int
     lib.ma_b200_selftest_wait_expiry.argtypes = [pp, C.c_void_p, C.c_size_t, C.c_void_p]
     lib.ma_b200_selftest_wait_expiry.restype = C.c_int
+    lib.ma_b200_selftest_generic_general_form.argtypes = [C.c_int]
+    lib.ma_b200_selftest_generic_general_form.restype = None
     lib.ma_b200_status_string.argtypes = [C.c_int]
     lib.ma_b200_status_string.restype = C.c_char_p
     lib.ma_b200_last_error.argtypes = []

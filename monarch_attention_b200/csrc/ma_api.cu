@@ -279,6 +279,8 @@ int ma_b200_poll_device_status(int device) {
   return MA_B200_OK;
 }
 
+void ma_b200_selftest_generic_general_form(int on) { ma::generic_set_general_form_only(on); }
+
 int ma_b200_selftest_wait_expiry(const ma_b200_problem* p, void* workspace, size_t workspace_bytes, void* stream_v) {
   int rc = validate(p, true);
   if (rc != MA_B200_OK) return rc;

@@ -67,6 +67,8 @@ __device__ __forceinline__ float round_through(float x) {
 
 // Host-side launchers implemented by the kernel translation units.
 // Each returns cudaSuccess or the launch error.
+// Test hook: 1 = the generic family always runs its general (warp-per-row) form.
+void generic_set_general_form_only(int on);
 cudaError_t launch_generic_stage(const Geometry& g, int qk_dtype, int v_dtype, StageKind kind, bool first,
                                  cudaStream_t stream);
 size_t generic_stage_smem_bytes(const Geometry& g, StageKind kind);

@@ -540,7 +540,9 @@ __global__ void __launch_bounds__(256) small_output_kernel(const Geometry g) {
 size_t small_smem_bytes(const Geometry& g) {
   return ((size_t)kSmallMax * (2 * (g.D + 1) + (g.Dv + 1)) + kSmallMax * 17) * sizeof(float);
 }
+int g_general_form_only = 0;  // test hook: 1 = never take the small-tile kernels
 bool small_tiles(const Geometry& g) {
+  if (g_general_form_only) return false;
   return g.B <= kSmallMax && g.M <= kSmallMax && small_smem_bytes(g) <= 48 * 1024;
 }
 
@@ -608,6 +610,8 @@ cudaError_t launch_typed(const Geometry& g, StageKind kind, bool first, cudaStre
 }
 
 }  // namespace
+
+void generic_set_general_form_only(int on) { g_general_form_only = on ? 1 : 0; }
 
 size_t generic_stage_smem_bytes(const Geometry& g, StageKind kind) {
   const size_t keys = (kind == kStageRight || kind == kStageRightWithV) ? g.B : g.M;

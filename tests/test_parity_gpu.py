@@ -310,6 +310,32 @@ def test_expired_device_wait_is_reported_and_harmless(ma):
     assert torch.equal(again, good)
 
 
+def test_generic_small_tile_form_returns_the_bits_of_the_general_form(ma):
+    """Tiles of up to 16 x 16 run thread-per-logit kernels; they form every product and every sum in the
+    order of the general warp-per-row kernels, so the two must agree bit for bit (fp32, 16-bit, masks,
+    front padding, odd widths, several iterations)."""
+    from monarch_attention_b200 import _cabi
+    lib = _cabi.load()
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(1)
+    shapes = [(2, 12, 256, 64, 64, 16, 1, torch.float32, "post", False), (2, 3, 250, 64, 64, 16, 2, torch.float32, "pre", True),
+              (1, 4, 197, 64, 64, 15, 3, torch.bfloat16, "pre", False), (2, 2, 100, 33, 40, 10, 2, torch.float16, "post", True),
+              (1, 2, 144, 80, 80, 12, 2, torch.bfloat16, "post", True)]
+    try:
+        for E, H, N, D, Dv, B, T, dt, pad, masked in shapes:
+            q, k = (torch.randn(E, H, N, D, generator=g).to(dt).to(dev) for _ in range(2))
+            v = torch.randn(E, H, N, Dv, generator=g).to(dt).to(dev)
+            mask = (torch.rand(E, N, generator=g) > 0.2).to(dev) if masked else None
+            mod = ma.MonarchAttention(B, T, pad, impl="b200-generic")
+            lib.ma_b200_selftest_generic_general_form(0)
+            small = mod(q, k, v, mask)
+            lib.ma_b200_selftest_generic_general_form(1)
+            general = mod(q, k, v, mask)
+            assert torch.equal(small.view(torch.uint8), general.view(torch.uint8)), (E, H, N, D, Dv, B, T, dt)
+    finally:
+        lib.ma_b200_selftest_generic_general_form(0)
+
+
 def test_requires_grad_inputs_are_refused(ma):
     dev = torch.device("cuda:0")
     q = torch.randn(1, 2, 32, 16, device=dev, requires_grad=True)
