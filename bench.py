@@ -445,24 +445,30 @@ def run_ours(args, rank, world, local):
     hout = torch.empty(outs[0].shape, dtype=outs[0].dtype).pin_memory()
     from monarch_attention_b200 import monarch_attention_b200_host
 
-    def e2e_step():
-        # the package's host-buffer entry point: chunks of heads, H2D / kernels / D2H on three streams;
-        # steps do not overlap one another (the caller's stream waits for the last D2H of every step)
-        monarch_attention_b200_host(hq, hk, hv, None, w["T"], w["B"], False, out=hout, wait=False,
+    def e2e_step(streamed):
+        # the package's host-buffer entry point: chunks of heads, H2D / kernels / D2H on three streams.
+        # streamed: the copy-in of a step starts while the kernels and the copy-out of the previous step are
+        # still running (every step still copies its own inputs in and its own result out); otherwise the
+        # steps do not overlap one another (the caller's stream waits for the last D2H of every step).
+        monarch_attention_b200_host(hq, hk, hv, None, w["T"], w["B"], False, out=hout, wait=False, streamed=streamed,
                                     heads_per_chunk=args.e2e_heads_per_chunk)
 
-    for _ in range(3):
-        e2e_step()
-    torch.cuda.synchronize()
-    barrier(world)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    e1.record()
-    torch.cuda.synchronize()
-    barrier(world)
-    e2e_ms = max_over_ranks(e0.elapsed_time(e1), world, dev) / e2e_steps
+    def time_e2e(streamed):
+        for _ in range(3):
+            e2e_step(streamed)
+        torch.cuda.synchronize()
+        barrier(world)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(e2e_steps):
+            e2e_step(streamed)
+        e1.record()
+        torch.cuda.synchronize()
+        barrier(world)
+        return max_over_ranks(e0.elapsed_time(e1), world, dev) / e2e_steps
+
+    e2e_serial_ms = time_e2e(False)
+    e2e_ms = time_e2e(True)
     h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv))
     d2h = hout.numel() * hout.element_size()
     sampler.stop()
@@ -574,8 +580,10 @@ def run_ours(args, rank, world, local):
         "clocks": sampler.summary(),
         "e2e": {"value": tokens_per_step / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps, "host_placement": numa,
-                "api": "monarch_attention_b200_host: pinned host q, k, v in, pinned host result out, "
-                       f"{args.e2e_heads_per_chunk} heads per chunk"},
+                "ms_per_step_without_overlap_between_steps": e2e_serial_ms,
+                "api": "monarch_attention_b200_host(streamed=True): pinned host q, k, v in, pinned host result out every "
+                       f"step, {args.e2e_heads_per_chunk} heads per chunk; the copy-in of a step overlaps the kernels and "
+                       "the copy-out of the step before it"},
         "gpu_launches": args.steps * (1 if fused else n_stage),
         "roofline": roofline,
         "cpu_baseline": cpu_baseline,

@@ -217,6 +217,14 @@ MA_B200_API const char* ma_b200_static_scratch_last_error(void);
 MA_B200_API size_t ma_b200_host_scratch_bytes(const ma_b200_problem* p, int heads_per_chunk);
 MA_B200_API int ma_b200_forward_host(const ma_b200_problem* p, int heads_per_chunk, void* device_scratch,
                                      size_t scratch_bytes, void* stream);
+/* The same for a stream of calls (no counterpart in the reference).  The host buffers of q, k, v (and the
+ * mask) must be valid when the call is made - nothing queued on `stream` is waited for before the copy-in
+ * starts - and when the previous call on this device used the same scratch with the same layout, this call's
+ * copy-in runs while that call's kernels and copy-out are still in flight, so that back-to-back calls keep
+ * the host-to-device link busy all the time.  `stream` is made to wait for this call's last kernel and last
+ * copy, as above; results arrive in call order. */
+MA_B200_API int ma_b200_forward_host_streamed(const ma_b200_problem* p, int heads_per_chunk, void* device_scratch,
+                                              size_t scratch_bytes, void* stream);
 MA_B200_API const char* ma_b200_host_last_error(void);
 
 MA_B200_API int32_t ma_b200_abi_version(void);

@@ -22,7 +22,7 @@ EXPORTS = (
     "ma_b200_workspace_bytes", "ma_b200_workspace_layout_of", "ma_b200_forward", "ma_b200_forward_timed",
     "ma_b200_device_status", "ma_b200_status_string", "ma_b200_last_error", "ma_b200_abi_version",
     "ma_b200_forward_static_scratch", "ma_b200_static_scratch_bytes", "ma_b200_static_scratch_last_error",
-    "ma_b200_host_scratch_bytes", "ma_b200_forward_host", "ma_b200_host_last_error",
+    "ma_b200_host_scratch_bytes", "ma_b200_forward_host", "ma_b200_forward_host_streamed", "ma_b200_host_last_error",
     "ma_b200_poll_device_status", "ma_b200_selftest_wait_expiry", "ma_b200_selftest_generic_general_form",
 )
 
@@ -93,6 +93,8 @@ def load() -> C.CDLL:
     lib.ma_b200_host_scratch_bytes.restype = C.c_size_t
     lib.ma_b200_forward_host.argtypes = [pp, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]
     lib.ma_b200_forward_host.restype = C.c_int
+    lib.ma_b200_forward_host_streamed.argtypes = [pp, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.ma_b200_forward_host_streamed.restype = C.c_int
     lib.ma_b200_host_last_error.argtypes = []
     lib.ma_b200_host_last_error.restype = C.c_char_p
     if lib.ma_b200_abi_version() != ABI_VERSION:

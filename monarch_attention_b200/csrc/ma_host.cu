@@ -28,6 +28,10 @@ struct Pipes {
   cudaStream_t in = nullptr, comp = nullptr, out = nullptr;
   cudaEvent_t start = nullptr, loaded[kSlots] = {}, computed[kSlots] = {}, stored[kSlots] = {}, done_comp = nullptr,
               done_out = nullptr;
+  // what the previous call on this device laid out in the scratch (a streamed call may only overlap a
+  // previous call that used the same slots)
+  const void* last_scratch = nullptr;
+  size_t last_slot_bytes = 0, last_total = 0;
 };
 Pipes g_pipes[kMaxDevices];
 std::mutex g_pipes_mutex;
@@ -137,8 +141,8 @@ MA_B200_API size_t ma_b200_host_scratch_bytes(const ma_b200_problem* p, int head
   return L.total;
 }
 
-MA_B200_API int ma_b200_forward_host(const ma_b200_problem* p, int heads_per_chunk, void* device_scratch,
-                                     size_t scratch_bytes, void* stream_v) {
+static int forward_host_impl(const ma_b200_problem* p, int heads_per_chunk, void* device_scratch, size_t scratch_bytes,
+                             void* stream_v, bool streamed) {
   g_host_error.clear();
   HostLayout L;
   int rc = host_layout(p, heads_per_chunk, &L, &g_host_error);
@@ -169,11 +173,24 @@ MA_B200_API int ma_b200_forward_host(const ma_b200_problem* p, int heads_per_chu
 #define MA_TRY(call, what) \
   if ((ce = (call)) != cudaSuccess) return fail(ce, what)
 
-  // everything below is ordered after what the caller has already queued on its stream
-  MA_TRY(cudaEventRecord(P->start, caller), "cudaEventRecord(start)");
-  MA_TRY(cudaStreamWaitEvent(P->in, P->start, 0), "cudaStreamWaitEvent(in, start)");
-  MA_TRY(cudaStreamWaitEvent(P->comp, P->start, 0), "cudaStreamWaitEvent(comp, start)");
-  MA_TRY(cudaStreamWaitEvent(P->out, P->start, 0), "cudaStreamWaitEvent(out, start)");
+  // A streamed call may start copying in while the previous call on this device is still computing and
+  // copying out, provided that call used the scratch in the same way (same slots: the per-slot events then
+  // order every reuse); anything else is ordered after what the caller has already queued on its stream,
+  // which includes the end of the previous call.
+  const bool overlap = streamed && P->last_scratch == device_scratch && P->last_slot_bytes == L.slot_bytes &&
+                       P->last_total == L.total;
+  P->last_scratch = device_scratch;
+  P->last_slot_bytes = L.slot_bytes;
+  P->last_total = L.total;
+  if (!overlap) {
+    MA_TRY(cudaEventRecord(P->start, caller), "cudaEventRecord(start)");
+    MA_TRY(cudaStreamWaitEvent(P->in, P->start, 0), "cudaStreamWaitEvent(in, start)");
+    MA_TRY(cudaStreamWaitEvent(P->comp, P->start, 0), "cudaStreamWaitEvent(comp, start)");
+    MA_TRY(cudaStreamWaitEvent(P->out, P->start, 0), "cudaStreamWaitEvent(out, start)");
+  } else if (p->mask != nullptr) {
+    // the mask has one place in the scratch: the previous call's kernels must have read theirs
+    MA_TRY(cudaStreamWaitEvent(P->in, P->done_comp, 0), "cudaStreamWaitEvent(in, done_comp)");
+  }
   unsigned char* mask_dev = nullptr;
   if (p->mask != nullptr) {
     mask_dev = reinterpret_cast<unsigned char*>(base + L.mask_off);
@@ -201,14 +218,14 @@ MA_B200_API int ma_b200_forward_host(const ma_b200_problem* p, int heads_per_chu
       char* sv = sk + L.qk_bytes;
       char* so = sv + L.v_bytes;
       // copy in: the kernels of the chunk that used this slot last have read q, k, v
-      if (i >= kSlots) MA_TRY(cudaStreamWaitEvent(P->in, P->computed[slot], 0), "wait(in, computed)");
+      if (i >= kSlots || overlap) MA_TRY(cudaStreamWaitEvent(P->in, P->computed[slot], 0), "wait(in, computed)");
       MA_TRY(copy_heads(sq, p->q, e, h0, nh, p->N, p->D, es_qk, true, P->in), "H2D q");
       MA_TRY(copy_heads(sk, p->k, e, h0, nh, p->N, p->D, es_qk, true, P->in), "H2D k");
       MA_TRY(copy_heads(sv, p->v, e, h0, nh, p->N, p->Dv, es_v, true, P->in), "H2D v");
       MA_TRY(cudaEventRecord(P->loaded[slot], P->in), "record(loaded)");
       // compute: inputs landed, and the previous result of this slot has left it
       MA_TRY(cudaStreamWaitEvent(P->comp, P->loaded[slot], 0), "wait(comp, loaded)");
-      if (i >= kSlots) MA_TRY(cudaStreamWaitEvent(P->comp, P->stored[slot], 0), "wait(comp, stored)");
+      if (i >= kSlots || overlap) MA_TRY(cudaStreamWaitEvent(P->comp, P->stored[slot], 0), "wait(comp, stored)");
       ma_b200_problem sub = *p;
       sub.E = 1;
       sub.H = nh;
@@ -237,6 +254,16 @@ MA_B200_API int ma_b200_forward_host(const ma_b200_problem* p, int heads_per_chu
   MA_TRY(cudaStreamWaitEvent(caller, P->done_out, 0), "wait(caller, done_out)");
 #undef MA_TRY
   return MA_B200_OK;
+}
+
+MA_B200_API int ma_b200_forward_host(const ma_b200_problem* p, int heads_per_chunk, void* device_scratch,
+                                     size_t scratch_bytes, void* stream_v) {
+  return forward_host_impl(p, heads_per_chunk, device_scratch, scratch_bytes, stream_v, false);
+}
+
+MA_B200_API int ma_b200_forward_host_streamed(const ma_b200_problem* p, int heads_per_chunk, void* device_scratch,
+                                              size_t scratch_bytes, void* stream_v) {
+  return forward_host_impl(p, heads_per_chunk, device_scratch, scratch_bytes, stream_v, true);
 }
 
 }  // extern "C"

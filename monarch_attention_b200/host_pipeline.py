@@ -42,7 +42,7 @@ def plan_chunks(E: int, H: int, heads_per_chunk: int) -> list[tuple[int, int, in
 
 def monarch_attention_b200_host(q: Tensor, k: Tensor, v: Tensor, attn_mask: Tensor | None, T: int, B: int,
                                 pre_pad: bool, *, out: Tensor | None = None, device=None,
-                                heads_per_chunk: int = 8, wait: bool = True,
+                                heads_per_chunk: int = 8, wait: bool = True, streamed: bool = False,
                                 kernel: int = _cabi.KERNEL_AUTO) -> Tensor:
     """Same computation as ``monarch_attention_b200`` for q, k, v (and the result) in host memory.
 
@@ -55,6 +55,10 @@ def monarch_attention_b200_host(q: Tensor, k: Tensor, v: Tensor, attn_mask: Tens
     wait:    block until the result is in ``out``; with ``wait=False`` the current stream has been made
              to wait for the last copy instead, and the caller synchronises it before reading ``out``
              (and keeps q, k, v, the mask and ``out`` alive until then).
+    streamed: for a sequence of calls with ``wait=False`` whose host inputs are already valid when each call
+             is made: the copy-in of a call starts while the kernels and the copy-out of the previous call
+             are still running (``ma_b200_forward_host_streamed``), so that the host-to-device link never
+             idles between calls.
     """
     _check_device_free_inputs(q, k, v, attn_mask)
     if q.is_cuda or k.is_cuda or v.is_cuda or (attn_mask is not None and attn_mask.is_cuda):
@@ -87,8 +91,8 @@ def monarch_attention_b200_host(q: Tensor, k: Tensor, v: Tensor, attn_mask: Tens
             torch.cuda.synchronize(device)  # an earlier call may still be using the old scratch
             scratch = _scratch[idx] = torch.empty(need, dtype=torch.uint8, device=device)
         stream = torch.cuda.current_stream(device)
-        rc = lib.ma_b200_forward_host(C.byref(prob), heads_per_chunk, scratch.data_ptr(), scratch.numel(),
-                                      stream.cuda_stream)
+        entry = lib.ma_b200_forward_host_streamed if streamed else lib.ma_b200_forward_host
+        rc = entry(C.byref(prob), heads_per_chunk, scratch.data_ptr(), scratch.numel(), stream.cuda_stream)
         if rc != 0:
             _cabi.raise_for_status(rc, lib.ma_b200_host_last_error().decode())
         if wait:

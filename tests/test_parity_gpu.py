@@ -336,6 +336,27 @@ def test_generic_small_tile_form_returns_the_bits_of_the_general_form(ma):
         lib.ma_b200_selftest_generic_general_form(0)
 
 
+def test_streamed_host_calls_overlap_without_mixing_their_data(ma):
+    """Back-to-back calls through the streamed host entry point (copy-in of a call while the previous call
+    still computes and copies out) must each return exactly what the device entry point returns for their own
+    inputs - also when the shape changes between calls, which turns the overlap off for that call."""
+    from monarch_attention_b200 import monarch_attention_b200, monarch_attention_b200_host
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(7)
+    shapes = [(1, 8, 1024, 64, 32)] * 4 + [(2, 4, 512, 64, 32)] * 2 + [(1, 8, 1024, 64, 32)] * 2
+    calls = []
+    for E, H, N, D, B in shapes:
+        q, k, v = (torch.randn(E, H, N, D, generator=g).to(torch.bfloat16).pin_memory() for _ in range(3))
+        mask = (torch.rand(E, N, generator=g) > 0.1).to(torch.uint8).pin_memory() if len(calls) % 2 else None
+        calls.append((q, k, v, mask, B, torch.empty_like(v).pin_memory()))
+    for q, k, v, mask, B, out in calls:
+        monarch_attention_b200_host(q, k, v, mask, 2, B, False, out=out, wait=False, streamed=True, heads_per_chunk=2)
+    torch.cuda.synchronize()
+    for q, k, v, mask, B, out in calls:
+        want = monarch_attention_b200(q.to(dev), k.to(dev), v.to(dev), None if mask is None else mask.to(dev), 2, B, False)
+        assert torch.equal(out, want.cpu())
+
+
 def test_requires_grad_inputs_are_refused(ma):
     dev = torch.device("cuda:0")
     q = torch.randn(1, 2, 32, 16, device=dev, requires_grad=True)
