@@ -125,8 +125,14 @@ def monarch_attention_b200(q: Tensor, k: Tensor, v: Tensor, attn_mask: Tensor | 
     """
     _check_inputs(q, k, v, attn_mask)
     if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
-        raise RuntimeError("monarch_attention_b200 is forward-only: call it under torch.no_grad() or on detached "
-                           "tensors (the reference's impl=\"torch\" is the differentiable path)")
+        # training: the kernels give the result, the gradients come from recomputation (backward.py)
+        if out is not None:
+            raise ValueError("out= cannot be combined with inputs that require a gradient")
+        from .backward import MonarchAttentionFunction
+        return MonarchAttentionFunction.apply(
+            q, k, v, attn_mask, T, B, pre_pad,
+            lambda a, b, c: monarch_attention_b200(a, b, c, attn_mask, T, B, pre_pad, kernel=kernel,
+                                                   token_major_output=token_major_output))
     lib = _cabi.load()
     dev_index = q.device.index if q.device.index is not None else torch.cuda.current_device()
     # A bounded wait of an earlier asynchronous call on this device that gave up is reported here, at the

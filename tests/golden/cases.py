@@ -199,3 +199,24 @@ def make_inputs(case):
         mask = (torch.rand(E, N, generator=g) > 0.4).to(torch.int64)
         mask[:, -1] = 1
     return q, k, v, mask
+
+
+# Cases whose gradients are stored (cotangent of the output = seeded weights): small enough for autograd through
+# the reference on the CPU.  The reference trains through exactly this path (its eager implementation under
+# autograd); the library's gradients are held to these.
+GRAD_CASES = [
+    _c("grad_f32_t2", 1, 2, 32, 16, 8, 2, False, "f32"),
+    _c("grad_f32_mask_prepad_t3", 2, 2, 29, 16, 8, 3, True, "f32", mask="block_safe"),
+    _c("grad_f32_t1_ragged", 1, 3, 50, 24, 16, 1, False, "f32"),
+    _c("grad_bf16_t2", 1, 2, 64, 32, 8, 2, False, "bf16", scale="rsqrt_d"),
+    _c("grad_f16_mask_t2", 2, 2, 48, 16, 8, 2, False, "f16", mask="block_safe", scale="rsqrt_d"),
+    _c("grad_bf16_n4096_b64_t2", 1, 1, 4096, 64, 64, 2, False, "bf16", scale="rsqrt_d"),
+]
+GRAD_CASES_BY_NAME = {c["name"]: c for c in GRAD_CASES}
+
+
+def grad_weights(case):
+    """Seeded cotangent for the output of a case (float32, shape of the output)."""
+    g = torch.Generator(device="cpu")
+    g.manual_seed((zlib.crc32(case["name"].encode()) ^ 0x5bd1e995) & 0x7FFFFFFF)
+    return torch.randn(case["E"], case["H"], case["N"], case["Dv"], generator=g, dtype=torch.float32)

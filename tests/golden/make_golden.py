@@ -16,6 +16,11 @@ inputs and stores
                    patterns);
 * ``<name>/sums``  float64 per-(e,h) sums and sums of squares of the full output;
 * ``<name>/qsum``  float64 sum of q, k, v (guards the input generator).
+
+For the cases of ``GRAD_CASES`` it also differentiates the reference (autograd through its eager
+implementation, the way the reference trains) with the seeded cotangent ``grad_weights(case)`` and stores
+``<name>/out`` and ``<name>/dq``, ``<name>/dk``, ``<name>/dv`` (bit patterns; all elements of a small
+tensor, a fixed strided sample of 2**14 positions of a large one).
 """
 from __future__ import annotations
 
@@ -28,7 +33,7 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
-from cases import CASES, make_inputs  # noqa: E402
+from cases import CASES, GRAD_CASES, grad_weights, make_inputs  # noqa: E402
 
 FULL_LIMIT = 1 << 17
 SAMPLE = 1 << 16
@@ -46,6 +51,13 @@ def sample_positions(numel: int) -> np.ndarray:
         return np.arange(numel)
     step = numel / SAMPLE
     return (np.arange(SAMPLE) * step).astype(np.int64)
+
+
+def grad_sample_positions(numel: int) -> np.ndarray:
+    """All positions of a small tensor, a fixed strided sample of 2**14 of a large one."""
+    if numel <= (1 << 15):
+        return np.arange(numel)
+    return (np.arange(1 << 14) * (numel / (1 << 14))).astype(np.int64)
 
 
 def summarize(out: torch.Tensor) -> dict:
@@ -78,6 +90,17 @@ def main():
         blob[f"{case['name']}/qsum"] = np.array(
             [x.to(torch.float64).sum().item() for x in (q, k, v)], dtype=np.float64)
         print(f"{case['name']:36s} out {tuple(out.shape)} {out.dtype}")
+    for case in GRAD_CASES:
+        q, k, v, mask = make_inputs(case)
+        q, k, v = (t.requires_grad_(True) for t in (q, k, v))
+        mod = MonarchAttention(case["B"], case["T"], "pre" if case["pre_pad"] else "post", impl="torch")
+        out = mod(q, k, v, mask)
+        out.backward(grad_weights(case).to(out.dtype))
+        for key, t in (("out", out.detach()), ("dq", q.grad), ("dk", k.grad), ("dv", v.grad)):
+            assert torch.isfinite(t.float()).all(), (case["name"], key)
+            flat = to_bits(t).reshape(-1)
+            blob[f"{case['name']}/{key}"] = flat[grad_sample_positions(flat.size)]
+        print(f"{case['name']:36s} out {tuple(out.shape)} {out.dtype} + gradients")
     np.savez_compressed(args.out, **blob)
     print("wrote", args.out, os.path.getsize(args.out), "bytes")
 

@@ -357,16 +357,6 @@ def test_streamed_host_calls_overlap_without_mixing_their_data(ma):
         assert torch.equal(out, want.cpu())
 
 
-def test_requires_grad_inputs_are_refused(ma):
-    dev = torch.device("cuda:0")
-    q = torch.randn(1, 2, 32, 16, device=dev, requires_grad=True)
-    mod = ma.MonarchAttention(8, 2, "post")
-    with pytest.raises(RuntimeError, match="forward-only"):
-        mod(q, q, q)
-    with torch.no_grad():
-        assert mod(q, q, q).shape == q.shape
-
-
 # ---- full benchmark size: properties that need no CPU oracle run ---------------------------
 
 @pytest.fixture(scope="module")
