@@ -254,6 +254,24 @@ def test_get_matrix_is_row_stochastic_and_matches_oracle(ma):
     assert error_metrics(a.double().cpu().numpy(), ref.double().numpy())[2] < 1e-2
 
 
+def test_get_matrix_at_the_vit_shape(ma):
+    """The explicit attention matrix at the visualisation script's shape (reference:
+    experiments/vit/visualize_attentions.py:61-69; 197 tokens, b = 14, front padding, fp16 q and k): rows sum to
+    one, and multiplying it with V reproduces the module's output."""
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(11)
+    q, k, v = (torch.randn(2, 3, 197, 64, generator=g).mul(0.5).half().to(dev) for _ in range(3))
+    mod = ma.MonarchAttention(14, 2, "pre")
+    a = mod.get_matrix(q, k)
+    assert a.dtype == torch.float32 and a.shape == (2, 3, 197, 197)
+    assert torch.allclose(a.sum(-1), torch.ones_like(a.sum(-1)), atol=2e-3)
+    want = mod(q, k, v).float()
+    got = torch.matmul(a, v.float())
+    assert error_metrics(got.cpu().numpy(), want.cpu().numpy())[2] < 4e-3
+    ref = monarch_attention_oracle(q.cpu(), k.cpu(), torch.eye(197).expand(2, 3, 197, 197).contiguous(), None, 2, 14, True)
+    assert error_metrics(a.double().cpu().numpy(), ref.double().numpy())[2] < 4e-3
+
+
 def test_module_errors_on_gpu(ma):
     dev = torch.device("cuda:0")
     q = torch.zeros(1, 2, 32, 16, device=dev)
