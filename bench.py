@@ -604,12 +604,15 @@ def run_layer(args):
     from monarch_attention_b200 import _cabi
     from monarch_attention_b200.monarch_attention import make_problem
     f = args.layer.split(",")
+    dtype = torch.bfloat16
+    if f[-1] in ("f32", "f16", "bf16"):
+        dtype = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[f.pop()]
     E, H, N, D, B, T = (int(x) for x in f[:6])
     pre = len(f) > 6 and f[6] == "pre"
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     g = torch.Generator().manual_seed(0)
-    q, k, v = (torch.randn(E, H, N, D, generator=g).to(torch.bfloat16).to(dev) for _ in range(3))
+    q, k, v = (torch.randn(E, H, N, D, generator=g).div(8).to(dtype).to(dev) for _ in range(3))
     mask = (torch.rand(E, N, generator=g) > 0.1).to(torch.uint8).to(dev) if len(f) > 7 and f[7] == "mask" else None
     out = torch.empty_like(v)
     lib = _cabi.load()
@@ -641,7 +644,7 @@ def main():
                     help="weak: the full 16-head call on every rank; strong: the 16 heads of one call split across ranks")
     ap.add_argument("--e2e-heads-per-chunk", type=int, default=8,
                     help="heads per pipeline chunk of the end-to-end (host memory) measurement")
-    ap.add_argument("--layer", default=None, help="E,H,N,D,B,T,pre|post[,mask]: time one layer of that shape instead")
+    ap.add_argument("--layer", default=None, help="E,H,N,D,B,T,pre|post[,mask][,f32|f16|bf16]: time one layer of that shape instead (bf16 by default)")
     args = ap.parse_args()
     if args.layer:
         run_layer(args)
