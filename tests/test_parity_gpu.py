@@ -272,6 +272,34 @@ def test_get_matrix_at_the_vit_shape(ma):
     assert error_metrics(a.double().cpu().numpy(), ref.double().numpy())[2] < 4e-3
 
 
+@pytest.mark.parametrize("shape", [(1, 4, 4096, 64, 64, 2), (2, 3, 197, 64, 15, 1), (1, 2, 250, 24, 16, 2)],
+                         ids=["tcgen05-fused", "warp-mma", "generic"])
+def test_module_call_can_be_captured_in_a_cuda_graph(ma, shape):
+    """A call only queues stream-ordered work (a memset and the launches, the cooperative one included), so after
+    one ordinary call (which sizes the workspace and lets the library do its once-per-device set-up) it can be
+    captured in a CUDA graph and replayed on new contents of the same buffers."""
+    E, H, N, D, B, T = shape
+    dev = torch.device("cuda:0")
+    dt = torch.float32 if D == 24 else torch.bfloat16
+    g = torch.Generator().manual_seed(5)
+    draw = lambda: tuple((torch.randn(E, H, N, D, generator=g) / 8).to(dt).to(dev) for _ in range(3))
+    mod = ma.MonarchAttention(B, T, "pre")
+    q, k, v = draw()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        mod(q, k, v)                      # warm-up on the capturing stream
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        out = mod(q, k, v)
+    for _ in range(2):
+        q2, k2, v2 = draw()
+        q.copy_(q2); k.copy_(k2); v.copy_(v2)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, mod(q2, k2, v2))
+
+
 def test_module_errors_on_gpu(ma):
     dev = torch.device("cuda:0")
     q = torch.zeros(1, 2, 32, 16, device=dev)
