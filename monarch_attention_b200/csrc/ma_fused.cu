@@ -13,8 +13,8 @@
 // cl, y) of a head lives in one of G state slots; the next group reuses the slots (its first stage
 // waits for the last stage of the head that had the slot).  Every state tile is written once and read
 // once; its reader drops the tile's lines from L2 (discard.global.L2), so the state is never written
-// back to HBM, and q, k, v tiles are prefetched into L2 a few items ahead and marked evict-first on
-// their last use: HBM sees q, k, v once and the result once.
+// back to HBM, and q, k, v tiles are marked evict-first on their last use: HBM sees q, k, v once and the
+// result once.
 // The launch is cooperative so that every CTA of the grid is resident, which the in-order
 // item schedule needs for forward progress.
 //
@@ -266,9 +266,9 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
     // The warp works in batches of kBatch items: lane L < kBatch works out item n0 + L of this CTA (the
     // divisions of the schedule) and reads the completion counter it depends on, so that the latency of
     // those loads is paid once per batch (a longer batch would look further ahead than dependencies are
-    // complete); lanes kBatch .. 2 kBatch - 1 do the same for the batch after it, only to bring its q, k,
-    // v tiles into L2 ahead of time.  Then lane 0 takes the items one by one: ring accounts, descriptor,
-    // hand-off to the issuer.
+    // complete).  Then lane 0 takes the items one by one: ring accounts, descriptor, hand-off to the
+    // issuer.  (Prefetching the q, k, v tiles of the next batch into L2 from here was measured: the
+    // prefetch instructions queue in the TMA unit ahead of the loads that matter, and cost 1 - 8 %.)
     constexpr int kBatch = 4;
     int free_tiles = kRingTiles, oldest = 0, ring_pos = 0;  // ring accounting (lane 0): items [oldest, n) hold tiles
     int lefts = 0;                                          // left-factor items among them
@@ -282,8 +282,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
       const int my_n = n0 + lane;
       const int idx = (int)blockIdx.x + my_n * (int)gridDim.x;
       int w0 = 0, my_eh = 0, my_hs = 0, my_eh_hi = 0, dep_ok = 1;
-      int pf_kind = -1, pf_tile = 0;
-      if (lane < 2 * kBatch && my_n < n_items) {
+      if (lane < kBatch && my_n < n_items) {
         const int gi = idx / per_group;
         int r = idx - gi * per_group;
         int gh = min(args.group, EH - gi * args.group);
@@ -300,22 +299,11 @@ __global__ void __launch_bounds__(kThreads, 1) fused_kernel(const __grid_constan
         w0 = kind | ((stage == 0 ? 1 : 0) << 2) | (tile << 8) | (stage << 16);
         const int e = my_eh / g.H;
         my_eh_hi = (e << 16) | (my_eh - e * g.H);  // (batch element, head) of the user tensors
-        if (lane >= kBatch || n0 == 0) { pf_kind = kind; pf_tile = tile; }
-        if (args.wait_deps && lane < kBatch) {
+        if (args.wait_deps) {
           const int* ctr = nullptr;
           if (stage > 0) ctr = args.counters + my_eh * nst_all + (stage - 1);
           else if (args.reuse_slots && gi > 0) ctr = args.counters + (my_eh - args.group) * nst_all + (nst_all - 1);
           if (ctr != nullptr) dep_ok = ld_acquire_gpu(ctr) >= tph ? 1 : 0;
-        }
-      }
-      if (pf_kind >= 0) {
-        const int e = (int)((unsigned)my_eh_hi >> 16), h = my_eh_hi & 0xffff;
-        if (pf_kind == kStageRight || pf_kind == kStageRightWithV) {
-          if (w0 & 4) tma_prefetch_5d(&maps.q_blk, 0, 0, pf_tile, h, e);
-          tma_prefetch_5d(&maps.k_blk, 0, 0, pf_tile, h, e);
-          if (pf_kind == kStageRightWithV) tma_prefetch_5d(&maps.v_blk, 0, 0, pf_tile, h, e);
-        } else {
-          for (int jj = 0; jj < per; ++jj) tma_prefetch_5d(&maps.q_col, 0, pf_tile * per + jj, 0, h, e);
         }
       }
       __syncwarp();

@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the tensor-core kernels use:
-// mbarriers with bounded waits, TMA tensor loads and L2 prefetches, L2 eviction hints and line
+// mbarriers with bounded waits, TMA tensor loads, L2 eviction hints and line
 // discards, tcgen05 (mma, commit, ld, st, fences), the shared-memory matrix and instruction
 // descriptors, packed fp32-pair arithmetic, and 128-byte-swizzle address arithmetic.
 #pragma once
@@ -55,12 +55,6 @@ __device__ __forceinline__ void tma_load_5d_hint(uint32_t dst, const CUtensorMap
       "%3, %4, %5, %6}], [%7], %8;" ::"r"(dst),
       "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar), "l"(policy)
       : "memory");
-}
-// Bring a tile into L2 only.
-__device__ __forceinline__ void tma_prefetch_5d(const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4) {
-  asm volatile("cp.async.bulk.prefetch.tensor.5d.L2.global.tile [%0, {%1, %2, %3, %4, %5}];" ::"l"(map), "r"(c0), "r"(c1),
-               "r"(c2), "r"(c3), "r"(c4)
-               : "memory");
 }
 // L2 policy for data that will not be read again: first in line for eviction.
 __device__ __forceinline__ unsigned long long l2_policy_evict_first() {
